@@ -10,7 +10,8 @@ whether or not any mixer of the model declares such state.
 Token p of a request lives in page ``table[p // page_size]`` at offset ``p % page_size``
 (python/tandem/executor/forward_context.py:61).  Pages are taken when a step is about to run
 (``grow``), given back when the request ends (``end``), and, in a windowed group, as soon as
-the window of the request's next query has passed them; a released entry of the table is -1.
+the window of the request's next query has passed them (but for the pages of the first tokens
+that such a group keeps visible, ``KVNeed.keep_first``); a released entry of the table is -1.
 
 This file is bookkeeping only (no tensors); ``tandem_b200.cache.storage`` holds the memory.
 12vivi/tandem has one group and no state slots (python/tandem/scheduler/scheduler.py:130-139,
@@ -36,10 +37,15 @@ class KVNeed:
     num_kv_heads: int
     head_dim: int
     window: Optional[int] = None  # keys kept behind the newest one, itself included; None: all
+    value_dim: Optional[int] = None  # size of a value where it is not the key's
+    keep_first: int = 0  # tokens at the front of a request that stay visible behind the window
 
     @property
     def group_key(self) -> tuple:
-        return (self.num_kv_heads, self.head_dim, self.window)
+        if self.value_dim in (None, self.head_dim) and not (self.window and self.keep_first):
+            return (self.num_kv_heads, self.head_dim, self.window)
+        return (self.num_kv_heads, self.head_dim, self.window, self.value_dim or self.head_dim,
+                self.keep_first if self.window else 0)
 
 
 @dataclass
@@ -49,6 +55,7 @@ class Group:
     pool: PagePool
     window: Optional[int]
     tables: dict = field(default_factory=dict)  # request id -> list of page ids (-1: given back)
+    keep_first: int = 0  # tokens at the front whose pages a window never gives back
 
 
 @dataclass
@@ -73,7 +80,8 @@ class CacheManager:
                 continue
             if need.group_key not in by_key:
                 by_key[need.group_key] = len(self.groups)
-                self.groups.append(Group(need.group_key, [], PagePool(num_pages), need.window))
+                self.groups.append(Group(need.group_key, [], PagePool(num_pages), need.window,
+                                         keep_first=need.keep_first if need.window else 0))
             g = by_key[need.group_key]
             self.groups[g].runs.append(run)
             self.group_of_run[run] = g
@@ -117,6 +125,13 @@ class CacheManager:
             return 0
         return max(0, start - g.window + 1) // self.page_size
 
+    def _passed(self, g: Group, table: list, start: int) -> list:
+        """Indices of the pages that the window of a query at ``start`` has passed and that hold none
+        of the kept first tokens: what ``grow`` gives back."""
+        first = self._first_needed_page(g, start)
+        kept = cdiv(g.keep_first, self.page_size)
+        return [i for i in range(kept, min(first, len(table))) if table[i] >= 0]
+
     def pages_short(self, request_id: str, total_tokens: int) -> int:
         """How many pages are lacking, over all groups, to store ``total_tokens`` tokens of the
         request (0: ``grow`` will succeed).  Counts pages that ``grow`` would first give back."""
@@ -124,8 +139,7 @@ class CacheManager:
         short = 0
         for g in self.groups:
             table = g.tables[request_id]
-            first = self._first_needed_page(g, live.num_tokens)
-            freed = sum(1 for p in table[:first] if p >= 0)
+            freed = len(self._passed(g, table, live.num_tokens))
             need = cdiv(total_tokens, self.page_size) - len(table)
             short += max(0, need - (g.pool.num_free + freed))
         return short
@@ -137,8 +151,7 @@ class CacheManager:
         out = []
         for g in self.groups:
             table = g.tables[request_id]
-            first = self._first_needed_page(g, live.num_tokens)
-            freed = sum(1 for p in table[:first] if p >= 0)
+            freed = len(self._passed(g, table, live.num_tokens))
             out.append(max(0, cdiv(total_tokens, self.page_size) - len(table)) - freed)
         return out
 
@@ -151,8 +164,7 @@ class CacheManager:
             raise ValueError("a request cannot shrink")
         for g in self.groups:
             table = g.tables[request_id]
-            first = self._first_needed_page(g, live.num_tokens)
-            passed = [i for i in range(min(first, len(table))) if table[i] >= 0]
+            passed = self._passed(g, table, live.num_tokens)
             g.pool.release([table[i] for i in passed])
             for i in passed:
                 table[i] = -1

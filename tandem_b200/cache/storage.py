@@ -38,9 +38,9 @@ class CacheStorage:
         for run, need in enumerate(kv_needs):
             if need is None:
                 continue
-            shape = (pages, need.num_kv_heads, ps, need.head_dim)
-            self.k[run] = torch.zeros(shape, dtype=dtype, device=device)
-            self.v[run] = torch.zeros(shape, dtype=dtype, device=device)
+            self.k[run] = torch.zeros((pages, need.num_kv_heads, ps, need.head_dim), dtype=dtype, device=device)
+            self.v[run] = torch.zeros((pages, need.num_kv_heads, ps, need.value_dim or need.head_dim), dtype=dtype,
+                                      device=device)
             self.source_run[run] = run
         for run, other in enumerate(cache_of):
             if other is not None:

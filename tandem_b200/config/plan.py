@@ -87,6 +87,82 @@ class AttentionSpec(MixerSpec):
 
 
 @dataclass(frozen=True)
+class DistanceBiasSpec:
+    """A learned bias on attention scores by distance: ``table[bucket(i - j), head]`` with
+    ``buckets`` rows.  Distances below ``buckets // 2`` have a row each; from there on the rows
+    are spaced evenly in the logarithm of the distance up to ``max_distance``, and the last row
+    takes everything beyond: bucket(n) = min(buckets - 1, half + floor(ln(n / half) / ln(max_distance
+    / half) * (buckets - half))) with half = buckets // 2."""
+
+    buckets: int
+    max_distance: int
+
+    def bucket(self, n: int) -> int:
+        import math
+
+        half = self.buckets // 2
+        if n < half:
+            return n
+        return min(self.buckets - 1,
+                   half + int(math.floor(math.log(n / half) / math.log(self.max_distance / half) * (self.buckets - half))))
+
+
+@dataclass(frozen=True)
+class SinkAttentionSpec(MixerSpec):
+    """Grouped-query attention whose keys and values may differ in size, with these options, each
+    off where its field says so: projection biases; q and k divided by their root mean square per
+    head (no weight); scores capped by ``softcap * tanh(score / softcap)``; a learned bias by
+    distance; a window with ``keep_first`` tokens at the front of the sequence that stay visible;
+    a learned sink per head in the softmax denominator; values mixed with those that the first
+    layer of ``value_mix`` (a name shared by the layers that mix) made for the same token.
+    Checkpoint tensors: ``<prefix>.q``, ``.k``, ``.v``, ``.o`` (biases ``.q.b`` ...), ``.rel``
+    [buckets, heads], ``.sink`` [heads], ``.vmix`` []; ``names`` renames them (local -> suffix)."""
+
+    hidden_size: int = 0
+    num_heads: int = 0
+    num_kv_heads: int = 0
+    head_dim: int = 0  # of queries and keys
+    value_dim: int = 0
+    scale: float = 1.0
+    bias: bool = False
+    unit_norm: bool = False
+    norm_eps: float = 1e-6
+    softcap: Optional[float] = None
+    distance_bias: Optional[DistanceBiasSpec] = None
+    window: Optional[int] = None  # keys a query sees behind itself, itself included; None: all
+    keep_first: int = 0
+    sink: bool = False
+    value_mix: Optional[str] = None
+    value_mix_first: bool = False  # this layer's values are the ones the others mix in
+    names: tuple = ()
+
+
+@dataclass(frozen=True)
+class DecayRecurrenceSpec(MixerSpec):
+    """Linear attention with a fixed decay per head, kept as a float32 state per request:
+    S <- decay_h S + k v^T, o = S^T q.  ``activation``: on q, k and v ("none" | "silu");
+    ``rotary_dim`` / ``rotary_base``: rotate_half encoding of the first dims of q and k (0: none);
+    ``key_scale``: factor on k behind the rotation; ``output_norm``: "per_head" (each head divided by
+    its root mean square) or "all_heads" (one RMSNorm over the concatenated heads with the weight
+    ``<prefix>.norm``); ``gate``: activation of the output gate's own projection ("silu" | "sigmoid").
+    Checkpoint tensors: ``<prefix>.q``, ``.k``, ``.v``, ``.g``, ``.o``, ``.norm``."""
+
+    hidden_size: int = 0
+    num_heads: int = 0
+    key_dim: int = 0
+    value_dim: int = 0
+    decay: tuple = ()
+    activation: str = "none"
+    rotary_dim: int = 0
+    rotary_base: float = 10000.0
+    key_scale: float = 1.0
+    output_norm: str = "per_head"
+    gate: str = "silu"
+    norm_eps: float = 1e-6
+    names: tuple = ()
+
+
+@dataclass(frozen=True)
 class FeedForwardSpec(PartSpec):
     family = "feed_forward"
     prefix: str = ""
@@ -97,6 +173,18 @@ class GatedMLPSpec(FeedForwardSpec):
     hidden_size: int = 0
     intermediate_size: int = 0
     activation: str = "silu"
+
+
+@dataclass(frozen=True)
+class DenseMLPSpec(FeedForwardSpec):
+    """down(act(up(x))) with optional biases; ``activation``: "gelu_tanh" | "silu" | "none".
+    Checkpoint tensors ``<prefix>.up``, ``.down`` (biases ``.up.b``, ``.down.b``)."""
+
+    hidden_size: int = 0
+    intermediate_size: int = 0
+    activation: str = "gelu_tanh"
+    bias: bool = True
+    names: tuple = ()
 
 
 @dataclass(frozen=True)

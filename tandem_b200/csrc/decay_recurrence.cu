@@ -1,0 +1,204 @@
+// Linear attention with a fixed decay per head (no softmax, no denominator), carried as a state:
+//
+//   S_t = decay[h] * S_(t-1) + k_t v_t^T          S: [dk, dv] per head, float32, one per live request
+//   o_t = S_t^T q_t
+//
+// Three kernels, all float32 on the CUDA cores.  `decay_recurrence_prep` works in place on the raw
+// projection [q | k | v | ...] of each token: an activation on q, k and v (none or SiLU), the rotary
+// encoding of the first `rd` dims of every q and k head (dim i paired with i + rd/2; angle =
+// position * freq[i], in float32), and a constant factor on k after the rotation.
+// `decay_recurrence_scan` walks each request's tokens in order from the state its slot holds and
+// leaves the new state there.  The columns of S are independent, so a block owns 32 of them for one
+// (request, head); warp w of the block holds rows [32 w, 32 w + 32) of those columns in registers.
+// Tokens are staged sixteen at a time in shared memory; per token a thread does 32 updates of its
+// state and 32 multiply-adds of its part of o, and the parts of the warps are summed in warp order
+// after the sixteen.  The order of operations for a token never depends on how the request was cut
+// into steps or on the batch, so the state and the output are the same bits under any schedule.
+// `decay_recurrence_post` divides o by a root mean square (per head without weight, or over all
+// heads with a weight), multiplies by a gate (SiLU or sigmoid of its own projection) and rounds to
+// the storage type of the output projection's input.
+#include "common.cuh"
+
+namespace tb {
+
+constexpr int DR_CHUNK = 16;  // tokens staged at once
+
+__device__ __forceinline__ float act_apply(float x, int act) {
+  if (act == 1) return x / (1.f + expf(-x));  // SiLU
+  if (act == 2) return 1.f / (1.f + expf(-x));  // sigmoid
+  return x;
+}
+
+// One thread per (token, column) of the first 2 H dk + H dv columns.
+__global__ void decay_recurrence_prep_kernel(float* __restrict__ proj, int stride, const int* __restrict__ positions,
+                                             const float* __restrict__ freq, long long total, int cols, int H, int dk, int dv,
+                                             int rd, int act, float key_scale) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int half = rd >> 1;
+  for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (long long)gridDim.x * blockDim.x) {
+    const int t = (int)(idx / cols), c = (int)(idx % cols);
+    float* row = proj + (size_t)t * stride;
+    if (c >= 2 * H * dk) {  // v
+      if (act) row[c] = act_apply(row[c], act);
+      continue;
+    }
+    const bool is_k = c >= H * dk;
+    const float factor = is_k ? key_scale : 1.f;
+    const int d = c % dk;
+    if (d >= rd) {
+      row[c] = act_apply(row[c], act) * factor;
+    } else if (d < half) {  // this thread turns the pair (d, d + rd/2)
+      const float u = act_apply(row[c], act), v = act_apply(row[c + half], act);
+      const float a = (float)positions[t] * freq[d];
+      const float cs = cosf(a), sn = sinf(a);
+      row[c] = (u * cs - v * sn) * factor;
+      row[c + half] = (v * cs + u * sn) * factor;
+    }
+  }
+}
+
+// grid (ceil(dv / 32), H, requests); block = ceil(dk / 32) warps.
+__global__ void decay_recurrence_scan_kernel(const float* __restrict__ proj, int stride, const int* __restrict__ cu_seqlens,
+                                             const int* __restrict__ state_slots, float* __restrict__ state,
+                                             const float* __restrict__ decay, float* __restrict__ out, int H, int dk, int dv) {
+  extern __shared__ float smem[];
+  pdl_launch_dependents();
+  pdl_wait();
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  const int dkp = nw * 32;  // dk rounded up to whole warps
+  float* q_s = smem;                          // [DR_CHUNK][dkp]
+  float* k_s = q_s + DR_CHUNK * dkp;          // [DR_CHUNK][dkp]
+  float* v_s = k_s + DR_CHUNK * dkp;          // [DR_CHUNK][32]
+  float* part_s = v_s + DR_CHUNK * 32;        // [DR_CHUNK][nw][32]
+  const int h = blockIdx.y, b = blockIdx.z;
+  const int j = blockIdx.x * 32 + lane;       // this thread's column of S
+  const bool col_ok = j < dv;
+  const int t0 = cu_seqlens[b], t1 = cu_seqlens[b + 1];
+  if (t1 <= t0) return;
+  const float g = decay[h];
+  float* S = state + (((size_t)state_slots[b] * H + h) * dk) * dv;
+  float s[32];
+#pragma unroll
+  for (int i = 0; i < 32; ++i) {
+    const int d = w * 32 + i;
+    s[i] = (col_ok && d < dk) ? S[(size_t)d * dv + j] : 0.f;
+  }
+  const int q_col = h * dk, k_col = H * dk + h * dk, v_col = 2 * H * dk + h * dv + blockIdx.x * 32;
+  for (int c0 = t0; c0 < t1; c0 += DR_CHUNK) {
+    const int n = min(DR_CHUNK, t1 - c0);
+    for (int e = threadIdx.x; e < n * dkp; e += blockDim.x) {
+      const int c = e / dkp, d = e % dkp;
+      const float* row = proj + (size_t)(c0 + c) * stride;
+      q_s[e] = d < dk ? row[q_col + d] : 0.f;
+      k_s[e] = d < dk ? row[k_col + d] : 0.f;
+    }
+    for (int e = threadIdx.x; e < n * 32; e += blockDim.x) {
+      const int c = e >> 5, l = e & 31;
+      v_s[e] = (blockIdx.x * 32 + l < dv) ? proj[(size_t)(c0 + c) * stride + v_col + l] : 0.f;
+    }
+    __syncthreads();
+    for (int c = 0; c < n; ++c) {
+      const float vj = v_s[c * 32 + lane];
+      const float* kc = k_s + c * dkp + w * 32;
+      const float* qc = q_s + c * dkp + w * 32;
+      float part = 0.f;
+#pragma unroll
+      for (int i = 0; i < 32; ++i) {
+        s[i] = fmaf(kc[i], vj, g * s[i]);
+        part = fmaf(s[i], qc[i], part);
+      }
+      part_s[(c * nw + w) * 32 + lane] = part;
+    }
+    __syncthreads();
+    for (int c = w; c < n; c += nw) {  // the warps' parts in warp order
+      float o = 0.f;
+      for (int ww = 0; ww < nw; ++ww) o += part_s[(c * nw + ww) * 32 + lane];
+      if (col_ok) out[(size_t)(c0 + c) * H * dv + h * dv + j] = o;
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 32; ++i) {
+    const int d = w * 32 + i;
+    if (col_ok && d < dk) S[(size_t)d * dv + j] = s[i];
+  }
+}
+
+// One block per token.  mode 0: each head divided by its own root mean square; mode 1: all heads
+// together, times `weight` [H dv].  Then times gate_act(gate), rounded to T.
+template <typename T>
+__global__ void decay_recurrence_post_kernel(const float* __restrict__ o, const float* __restrict__ gate, int gate_stride,
+                                             const float* __restrict__ weight, T* __restrict__ y, int H, int dv, int mode,
+                                             int gate_act, float eps) {
+  __shared__ float scratch[33];
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x, lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  const float* orow = o + (size_t)t * H * dv;
+  const float* grow = gate ? gate + (size_t)t * gate_stride : nullptr;
+  T* yrow = y + (size_t)t * H * dv;
+  if (mode == 0) {
+    for (int h = w; h < H; h += nw) {
+      float ss = 0.f;
+      for (int d = lane; d < dv; d += 32) { const float x = orow[h * dv + d]; ss += x * x; }
+      ss = warp_sum(ss);
+      const float inv = rsqrtf(ss / (float)dv + eps);
+      for (int d = lane; d < dv; d += 32) {
+        const int c = h * dv + d;
+        yrow[c] = from_float<T>(orow[c] * inv * (grow ? act_apply(grow[c], gate_act) : 1.f));
+      }
+    }
+    return;
+  }
+  const int n = H * dv;
+  float ss = 0.f;
+  for (int c = threadIdx.x; c < n; c += blockDim.x) { const float x = orow[c]; ss += x * x; }
+  ss = block_sum(ss, scratch);
+  const float inv = rsqrtf(ss / (float)n + eps);
+  for (int c = threadIdx.x; c < n; c += blockDim.x)
+    yrow[c] = from_float<T>(orow[c] * inv * (weight ? weight[c] : 1.f) * (grow ? act_apply(grow[c], gate_act) : 1.f));
+}
+
+}  // namespace tb
+
+extern "C" {
+
+// proj float32 [T, stride]: columns [q: H dk | k: H dk | v: H dv | anything else].  freq [rd / 2] (rd 0: no rotation).
+int tb_decay_recurrence_prep(void* stream, float* proj, int stride, const int* positions, const float* freq, int T_tokens, int H,
+                             int dk, int dv, int rd, int act, float key_scale) {
+  if (T_tokens <= 0) return 0;
+  if (H <= 0 || dk <= 0 || dv <= 0 || rd < 0 || rd > dk || (rd & 1) || (rd && !freq) || act < 0 || act > 1) return TB_ERR_BAD_SIZE;
+  const int cols = 2 * H * dk + H * dv;
+  const long long total = (long long)T_tokens * cols;
+  long long blocks = (total + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  return tb::launch(tb::decay_recurrence_prep_kernel, dim3((int)blocks), dim3(256), 0, stream, proj, stride, positions, freq, total,
+                    cols, H, dk, dv, rd, act, key_scale);
+}
+
+// state float32 [slots, H, dk, dv]; out float32 [T, H dv]; cu_seqlens [requests + 1]; state_slots [requests].
+int tb_decay_recurrence_scan(void* stream, const float* proj, int stride, const int* cu_seqlens, const int* state_slots,
+                             float* state, const float* decay, float* out, int requests, int H, int dk, int dv) {
+  if (requests <= 0) return 0;
+  if (H <= 0 || dk <= 0 || dk > 1024 || dv <= 0 || H > 65535 || requests > 65535) return TB_ERR_BAD_SIZE;
+  const int nw = (dk + 31) / 32;
+  const size_t smem = (size_t)(2 * tb::DR_CHUNK * nw * 32 + tb::DR_CHUNK * 32 + tb::DR_CHUNK * nw * 32) * sizeof(float);
+  if (smem > 48 * 1024) {
+    const cudaError_t e = cudaFuncSetAttribute(tb::decay_recurrence_scan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+  }
+  return tb::launch(tb::decay_recurrence_scan_kernel, dim3((dv + 31) / 32, H, requests), dim3(nw * 32), smem, stream, proj, stride,
+                    cu_seqlens, state_slots, state, decay, out, H, dk, dv);
+}
+
+// o float32 [T, H dv]; gate float32 rows of H dv values (stride gate_stride) or null; weight [H dv] or null (mode 1).
+int tb_decay_recurrence_post(void* stream, const float* o, const float* gate, int gate_stride, const float* weight, void* y,
+                             int T_tokens, int H, int dv, int mode, int gate_act, float eps, int dtype) {
+  if (T_tokens <= 0) return 0;
+  if (H <= 0 || dv <= 0 || mode < 0 || mode > 1 || gate_act < 0 || gate_act > 2) return TB_ERR_BAD_SIZE;
+  TB_DISPATCH_DTYPE(dtype, tb::launch(tb::decay_recurrence_post_kernel<T>, dim3(T_tokens), dim3(256), 0, stream, o, gate, gate_stride,
+                                      weight, (T*)y, H, dv, mode, gate_act, eps));
+}
+
+}  // extern "C"

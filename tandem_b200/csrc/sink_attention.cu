@@ -1,0 +1,222 @@
+// Windowed attention with kept first tokens, a capped score, a learned bias by distance and a
+// softmax sink, over the paged cache; keys and values may have different sizes per head.
+//
+//   s(i, j) = cap * tanh(scale * (q_i . k_j) / cap) + bias[min(i - j, max_dist)][head]
+//   position i sees j  <=>  j <= i and (i - j < window or j < keep_first)        (window 0: all j <= i)
+//   o_i = sum_j exp(s(i, j)) v_j / (exp(sink[head]) + sum_j exp(s(i, j)))
+//
+// Every option is a run-time argument: cap 0 = no cap, bias null = none, sink null = none.  The bias
+// table is indexed by distance (the host expands whatever bucketing the model uses into one row per
+// distance up to the distance beyond which the bucket no longer changes).
+//
+// Two kernels.  `sink_attention_prep` takes the raw float32 projection [q | k | v] of each token,
+// adds the projection biases, divides each q and k head by its root mean square (no weight),
+// mixes v with the values another layer made for the same token (v <- (1 - l) v + l v_other), leaves
+// q and the unmixed v in place in float32 and writes k and the mixed v to the token's cache slot.
+// `sink_attention` then runs one warp per (token, query head) over the visible keys in ascending
+// order, 32 keys a turn, scores, softmax statistics and the output accumulator in float32: a
+// token's result does not depend on what else is in the batch, bit for bit.  The sink enters as the
+// starting state of the online softmax (running maximum = sink, running sum = 1, no value).
+#include "cache_layout.cuh"
+#include "common.cuh"
+
+namespace tb {
+
+constexpr int SA_MAX_DV = 512;
+constexpr int SA_WARPS = 4;
+
+// One warp per (token, unit): units 0..nh-1 are query heads, nh..nh+nkv-1 key heads, then value heads.
+template <typename T>
+__global__ void __launch_bounds__(128)
+sink_attention_prep_kernel(float* __restrict__ qkv, int stride, const float* __restrict__ bias,
+                           const float* __restrict__ v_other, int v_other_stride, const float* __restrict__ mix,
+                           const int* __restrict__ slots, T* __restrict__ k_cache, T* __restrict__ v_cache, int T_tokens, int nh,
+                           int nkv, int dk, int dv, int page_size, int unit_norm, float eps, int write_kv) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int lane = threadIdx.x & 31;
+  const int units = nh + 2 * nkv;
+  const long long g = (long long)blockIdx.x * 4 + (threadIdx.x >> 5);
+  if (g >= (long long)T_tokens * units) return;
+  const int t = (int)(g / units), u = (int)(g % units);
+  const int slot = (write_kv && slots) ? slots[t] : -1;
+  if (u < nh + nkv) {  // a query or key head: bias, then x / sqrt(mean(x^2) + eps)
+    const int col = u * dk;  // q heads, then k heads, lie one behind the other
+    float* row = qkv + (size_t)t * stride + col;
+    float ss = 0.f;
+    for (int d = lane; d < dk; d += 32) {
+      const float x = row[d] + (bias ? bias[col + d] : 0.f);
+      ss += x * x;
+    }
+    ss = warp_sum(ss);
+    const float inv = unit_norm ? rsqrtf(ss / (float)dk + eps) : 1.f;
+    if (u < nh) {
+      for (int d = lane; d < dk; d += 32) row[d] = (row[d] + (bias ? bias[col + d] : 0.f)) * inv;
+    } else if (slot >= 0) {
+      const int kvh = u - nh;
+      T* tile = k_cache + cache_tile(slot / page_size, kvh, nkv, page_size, dk);
+      const int r = slot % page_size;
+      for (int d = lane; d < dk; d += 32)
+        tile[cache_offset<T>(r, d, page_size, dk)] = from_float<T>((row[d] + (bias ? bias[col + d] : 0.f)) * inv);
+    }
+    return;
+  }
+  const int kvh = u - nh - nkv;
+  const int col = (nh + nkv) * dk + kvh * dv;
+  float* row = qkv + (size_t)t * stride + col;
+  const float l = v_other ? mix[0] : 0.f;
+  T* tile = slot >= 0 ? v_cache + cache_tile(slot / page_size, kvh, nkv, page_size, dv) : nullptr;
+  const int r = slot >= 0 ? slot % page_size : 0;
+  for (int d = lane; d < dv; d += 32) {
+    float x = row[d] + (bias ? bias[col + d] : 0.f);
+    row[d] = x;  // the layer's own values, for layers that mix them into theirs
+    if (v_other) x = (1.f - l) * x + l * v_other[(size_t)t * v_other_stride + kvh * dv + d];
+    if (tile) tile[cache_offset<T>(r, d, page_size, dv)] = from_float<T>(x);
+  }
+}
+
+// Dot product of the warp's query (shared memory, float32) with one key row of the cache.
+template <typename T>
+__device__ __forceinline__ float key_dot(const float* qs, const T* tile, int r, int dk, int page_size) {
+  float dot = 0.f;
+  if (sizeof(T) == 2 && (dk & 7) == 0) {  // eight elements = one 16-byte chunk, whole in either layout
+    for (int d = 0; d < dk; d += 8) {
+      const uint4 raw = *reinterpret_cast<const uint4*>(tile + cache_offset<T>(r, d, page_size, dk));
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float2 f = __bfloat1622float2(h[i]);
+        dot = fmaf(qs[d + 2 * i], f.x, dot);
+        dot = fmaf(qs[d + 2 * i + 1], f.y, dot);
+      }
+    }
+  } else if (sizeof(T) == 4 && (dk & 3) == 0) {
+    for (int d = 0; d < dk; d += 4) {
+      const float4 f = *reinterpret_cast<const float4*>(tile + cache_offset<T>(r, d, page_size, dk));
+      dot = fmaf(qs[d], f.x, dot);
+      dot = fmaf(qs[d + 1], f.y, dot);
+      dot = fmaf(qs[d + 2], f.z, dot);
+      dot = fmaf(qs[d + 3], f.w, dot);
+    }
+  } else {
+    for (int d = 0; d < dk; ++d) dot = fmaf(qs[d], to_float(tile[cache_offset<T>(r, d, page_size, dk)]), dot);
+  }
+  return dot;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(SA_WARPS * 32)
+sink_attention_kernel(const float* __restrict__ q, int q_stride, const T* __restrict__ k_cache, const T* __restrict__ v_cache,
+                      const int* __restrict__ block_table, int table_stride, const int* __restrict__ seq_of_token,
+                      const int* __restrict__ positions, T* __restrict__ out, int T_tokens, int nh, int nkv, int dk, int dv,
+                      int page_size, int window, int keep_first, float scale, float cap, const float* __restrict__ bias,
+                      int max_dist, const float* __restrict__ sink) {
+  extern __shared__ float smem[];  // SA_WARPS * dk floats: each warp's query
+  pdl_launch_dependents();
+  pdl_wait();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const long long g = (long long)blockIdx.x * SA_WARPS + warp;
+  if (g >= (long long)T_tokens * nh) return;
+  const int t = (int)(g / nh), h = (int)(g % nh);
+  const int kvh = h / (nh / nkv);
+  const int pos = positions[t];
+  const int* table = block_table + (size_t)seq_of_token[t] * table_stride;
+  float* qs = smem + warp * dk;
+  const float* qrow = q + (size_t)t * q_stride + (size_t)h * dk;
+  for (int d = lane; d < dk; d += 32) qs[d] = qrow[d];
+  __syncwarp();
+
+  constexpr int MAX_OWN = SA_MAX_DV / 32;  // value dims d = lane + 32 i of this lane
+  float acc[MAX_OWN];
+#pragma unroll
+  for (int i = 0; i < MAX_OWN; ++i) acc[i] = 0.f;
+  float m = sink ? sink[h] : -INFINITY, l = sink ? 1.f : 0.f;
+  const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+  const int kept = min(keep_first, lo);  // kept first tokens that the window no longer covers
+  const float inv_cap = cap > 0.f ? 1.f / cap : 0.f;
+
+  for (int seg = 0; seg < 2; ++seg) {
+    const int begin = seg ? lo : 0, end = seg ? pos + 1 : kept;
+    for (int base = begin; base < end; base += 32) {
+      const int key = base + lane;
+      long long tile = -1;  // element offset of the key's (page, kv head) tile, in rows (scaled by the row size where it is used)
+      int r_in = 0;
+      float s = -INFINITY;
+      if (key < end) {
+        const int page = table[key / page_size];
+        if (page >= 0) {
+          tile = (long long)page * nkv + kvh;
+          r_in = key % page_size;
+          s = key_dot<T>(qs, k_cache + tile * page_size * dk, r_in, dk, page_size) * scale;
+          if (cap > 0.f) s = cap * tanhf(s * inv_cap);
+          if (bias) s += bias[(size_t)min(pos - key, max_dist) * nh + h];
+        }
+      }
+      const float m_new = fmaxf(m, warp_max(s));
+      const float corr = (m == -INFINITY) ? 0.f : expf(m - m_new);
+      const float p = (tile >= 0) ? expf(s - m_new) : 0.f;
+      l = l * corr + warp_sum(p);
+      m = m_new;
+#pragma unroll
+      for (int i = 0; i < MAX_OWN; ++i) acc[i] *= corr;
+      const int count = min(32, end - base);
+      for (int j = 0; j < count; ++j) {
+        const float pj = __shfl_sync(0xffffffffu, p, j);
+        const long long tj = __shfl_sync(0xffffffffu, tile, j);
+        const int rin = __shfl_sync(0xffffffffu, r_in, j);
+        if (tj < 0) continue;  // the same in every lane
+        const T* vr = v_cache + tj * page_size * dv;
+#pragma unroll
+        for (int i = 0; i < MAX_OWN; ++i) {
+          const int d = lane + 32 * i;
+          if (d < dv) acc[i] = fmaf(pj, to_float(vr[cache_offset<T>(rin, d, page_size, dv)]), acc[i]);
+        }
+      }
+    }
+  }
+  const float inv = l > 0.f ? 1.f / l : 0.f;
+  T* orow = out + (size_t)t * nh * dv + (size_t)h * dv;
+#pragma unroll
+  for (int i = 0; i < MAX_OWN; ++i) {
+    const int d = lane + 32 * i;
+    if (d < dv) orow[d] = from_float<T>(acc[i] * inv);
+  }
+}
+
+}  // namespace tb
+
+extern "C" {
+
+// qkv float32 [T, stride >= nh dk + nkv dk + nkv dv]; bias float32 [nh dk + nkv dk + nkv dv] or null;
+// v_other float32 rows of nkv dv values (stride v_other_stride) with mix[0] their share, or null;
+// caches of the storage type `dtype`: K [pages, nkv, page_size, dk], V [pages, nkv, page_size, dv].
+int tb_sink_attention_prep(void* stream, float* qkv, int stride, const float* bias, const float* v_other, int v_other_stride,
+                           const float* mix, const int* slots, void* k_cache, void* v_cache, int T_tokens, int nh, int nkv, int dk,
+                           int dv, int page_size, int unit_norm, float eps, int write_kv, int dtype) {
+  if (T_tokens <= 0) return 0;
+  if (nh <= 0 || nkv <= 0 || dk <= 0 || dv <= 0 || page_size <= 0 || (v_other && !mix)) return TB_ERR_BAD_SIZE;
+  const long long warps = (long long)T_tokens * (nh + 2 * nkv);
+  const int blocks = (int)((warps + 3) / 4);
+  TB_DISPATCH_DTYPE(dtype, tb::launch(tb::sink_attention_prep_kernel<T>, dim3(blocks), dim3(128), 0, stream, qkv, stride, bias, v_other,
+                                      v_other_stride, mix, slots, (T*)k_cache, (T*)v_cache, T_tokens, nh, nkv, dk, dv, page_size,
+                                      unit_norm, eps, write_kv));
+}
+
+int tb_sink_attention(void* stream, const float* q, int q_stride, const void* k_cache, const void* v_cache, const int* block_table,
+                      int table_stride, const int* seq_of_token, const int* positions, void* out, int T_tokens, int nh, int nkv,
+                      int dk, int dv, int page_size, int window, int keep_first, float scale, float cap, const float* bias,
+                      int max_dist, const float* sink, int dtype) {
+  if (T_tokens <= 0) return 0;
+  if (dk <= 0 || dv <= 0 || dv > tb::SA_MAX_DV || dk > 2048 || nkv <= 0 || nh % nkv != 0 || page_size <= 0 || window < 0 ||
+      keep_first < 0 || (bias && max_dist < 0))
+    return TB_ERR_BAD_SIZE;
+  const long long warps = (long long)T_tokens * nh;
+  const int blocks = (int)((warps + tb::SA_WARPS - 1) / tb::SA_WARPS);
+  const size_t smem = (size_t)tb::SA_WARPS * dk * sizeof(float);
+  TB_DISPATCH_DTYPE(dtype, tb::launch(tb::sink_attention_kernel<T>, dim3(blocks), dim3(tb::SA_WARPS * 32), smem, stream, q, q_stride,
+                                      (const T*)k_cache, (const T*)v_cache, block_table, table_stride, seq_of_token, positions,
+                                      (T*)out, T_tokens, nh, nkv, dk, dv, page_size, window, keep_first, scale, cap, bias, max_dist,
+                                      sink));
+}
+
+}  // extern "C"

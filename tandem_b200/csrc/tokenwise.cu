@@ -440,6 +440,36 @@ __global__ void scale_softcap_kernel(float* __restrict__ x, long long n, float s
   }
 }
 
+// ---------------------------------------------------------------------------------------------
+// y[t, c] = act(x[t, c] + bias[c]) for a float32 product x, rounded to T.  act 0: none, 1: the tanh
+// form of GELU, 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))), 2: SiLU.  bias may be null.
+template <typename T>
+__global__ void bias_act_kernel(const float* __restrict__ x, const float* __restrict__ bias, T* __restrict__ y, long long total,
+                                int N, int act) {
+  pdl_launch_dependents();
+  pdl_wait();
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    float z = x[i] + (bias ? bias[i % N] : 0.f);
+    if (act == 1) z = 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+    else if (act == 2) z = z / (1.f + expf(-z));
+    y[i] = from_float<T>(z);
+  }
+}
+
+// residual[t, c] += (a[t, c] + a_bias[c]) + (b[t, c] + b_bias[c]): the outputs of two sublayers that
+// read the same normalised input enter the float32 stream in one pass.  b and either bias may be null.
+__global__ void add_pair_kernel(float* __restrict__ residual, const float* __restrict__ a, const float* __restrict__ a_bias,
+                                const float* __restrict__ b, const float* __restrict__ b_bias, long long total, int N) {
+  pdl_launch_dependents();
+  pdl_wait();
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const int c = (int)(i % N);
+    float s = a[i] + (a_bias ? a_bias[c] : 0.f);
+    if (b) s += b[i] + (b_bias ? b_bias[c] : 0.f);
+    residual[i] += s;
+  }
+}
+
 }  // namespace tb
 
 extern "C" {
@@ -505,6 +535,24 @@ int tb_silu_mul(void* stream, const void* gu, void* out, int T_tokens, int I, in
   long long blocks = (total + 255) / 256;
   if (blocks > 148 * 16) blocks = 148 * 16;
   TB_DISPATCH_DTYPE(dtype, tb::launch(tb::silu_mul_kernel<T>, dim3((int)blocks), dim3(256), 0, stream, (const T*)gu, (T*)out, total, I));
+}
+
+int tb_bias_act(void* stream, const float* x, const float* bias, void* y, int rows, int N, int act, int dtype) {
+  const long long total = (long long)rows * N;
+  if (total <= 0) return 0;
+  if (act < 0 || act > 2) return TB_ERR_BAD_SIZE;
+  long long blocks = (total + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  TB_DISPATCH_DTYPE(dtype, tb::launch(tb::bias_act_kernel<T>, dim3((int)blocks), dim3(256), 0, stream, x, bias, (T*)y, total, N, act));
+}
+
+int tb_add_pair(void* stream, float* residual, const float* a, const float* a_bias, const float* b, const float* b_bias, int rows,
+                int N) {
+  const long long total = (long long)rows * N;
+  if (total <= 0) return 0;
+  long long blocks = (total + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  return tb::launch(tb::add_pair_kernel, dim3((int)blocks), dim3(256), 0, stream, residual, a, a_bias, b, b_bias, total, N);
 }
 
 }  // extern "C"

@@ -38,7 +38,10 @@ def load_model(folder: str, dtype: str = "bfloat16", device="cuda:0") -> tuple[D
     cfg_dict = read_config_json(folder)
     arch = resolve_architecture(cfg_dict)
     cfg = arch.config_class.from_dict(cfg_dict)
-    return Decoder(arch.build_plan(cfg), SafetensorsFolder(folder), DTYPES[dtype], require_cuda(device)), cfg
+    source = SafetensorsFolder(folder)
+    if arch.complete is not None:  # sizes that the file leaves to the tensors' shapes
+        cfg = arch.complete(cfg, source.shapes())
+    return Decoder(arch.build_plan(cfg), source, DTYPES[dtype], require_cuda(device)), cfg
 
 
 def random_model(config: dict, seed: int = 0, dtype: str = "bfloat16", device="cuda:0",
@@ -75,7 +78,7 @@ class _Lazy(TensorSource):
 
 def kv_bytes_per_token(decoder: Decoder) -> int:
     elem = torch.empty((), dtype=decoder.dtype).element_size()
-    return sum(2 * n.num_kv_heads * n.head_dim * elem for n in decoder.kv_needs() if n is not None)
+    return sum(n.num_kv_heads * (n.head_dim + (n.value_dim or n.head_dim)) * elem for n in decoder.kv_needs() if n is not None)
 
 
 def build_executor(decoder: Decoder, page_size: int = 16, num_pages: Optional[int] = None,

@@ -22,6 +22,7 @@ from tandem_b200.cache.manager import cdiv
 
 
 ROUNDING = 64  # --max-tokens counts every live request rounded up to a multiple of this
+MAX_LIVE = 4  # requests that a trace has live at any time: the state tensors have this many rows
 
 
 def pool_pages(max_tokens: int, page_size: int) -> int:
@@ -47,7 +48,7 @@ def replay(model: str, dtype: str, out_dir: str, max_tokens: int, lines, device:
     os.makedirs(out_dir, exist_ok=True)
     decoder, _ = load_model(model, dtype, device)
     executor = build_executor(decoder, page_size=page_size, num_pages=pool_pages(max_tokens, page_size),
-                              max_requests=64)
+                              max_requests=MAX_LIVE)
     steps = 0
     for line in lines:
         line = line.strip()

@@ -15,6 +15,10 @@ that travels between the parts of a layer must be allowed to be *not computed ye
                    norm returns, after it has had the pending product added into the residual by the
                    product's own kernel, when the part behind it takes such input.
 
+``Unsummed``       a float32 product whose bias has not been added: what a mixer or feed-forward with
+                   an output bias returns when asked, so that the arrangement adds product and bias
+                   into the float32 residual in one pass, without a rounding in between.
+
 Only parts that say ``takes_deferred = True`` ever meet one of these; everything else gets tensors
 (``tensor`` computes what is pending with the stand-alone kernels).  12vivi/tandem fuses the same
 pair into its small-batch product (python/tandem/layers/triton_gemv.py:92-145,356-378).
@@ -53,8 +57,19 @@ class PendingNorm:
         return tuple(self.residual.shape)
 
 
+@dataclass
+class Unsummed:
+    product: torch.Tensor  # [M, N] float32
+    bias: Optional[torch.Tensor]  # [N] float32
+    out_dtype: torch.dtype  # what ``tensor`` rounds product + bias to
+
+    @property
+    def shape(self) -> tuple:
+        return tuple(self.product.shape)
+
+
 def is_pending(v: Any) -> bool:
-    return isinstance(v, (PendingLinear, PendingNorm))
+    return isinstance(v, (PendingLinear, PendingNorm, Unsummed))
 
 
 def tensor(v: Any) -> Optional[torch.Tensor]:
@@ -67,4 +82,6 @@ def tensor(v: Any) -> Optional[torch.Tensor]:
         return ops.linear(v.x, v.weight)
     if isinstance(v, PendingNorm):
         return ops.add_rmsnorm(None, v.residual, v.weight, v.eps, v.out_dtype)
+    if isinstance(v, Unsummed):
+        return ops.bias_act(v.product, v.bias, "none", v.out_dtype)
     raise TypeError(f"{type(v).__name__} stands for no tensor")

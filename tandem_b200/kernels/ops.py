@@ -259,6 +259,49 @@ def silu_mul(gate_up: torch.Tensor) -> torch.Tensor:
     return out
 
 
+_ACTIVATIONS = {"none": 0, "gelu_tanh": 1, "silu": 2}
+
+
+def bias_act(x: torch.Tensor, bias: Optional[torch.Tensor], activation: str, out_dtype: torch.dtype) -> torch.Tensor:
+    """act(x + bias) for a float32 product x [M, N], rounded to ``out_dtype``.  ``activation``: "none",
+    "gelu_tanh" (0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3)))) or "silu"; ``bias`` [N] float32 or None."""
+    _need(x, "x", torch.float32)
+    if activation not in _ACTIVATIONS:
+        raise KernelError(f"no activation {activation!r} (have {sorted(_ACTIVATIONS)})")
+    M, N = x.shape
+    if bias is not None:
+        _need(bias, "bias", torch.float32)
+        if bias.numel() != N:
+            raise KernelError(f"bias has {bias.numel()} elements, rows have {N}")
+    y = torch.empty((M, N), dtype=out_dtype, device=x.device)
+    lib = load_library("tokenwise")
+    _check(lib.tb_bias_act(_stream(), _ptr(x), _ptr(bias), _ptr(y), M, N, _ACTIVATIONS[activation], _code(out_dtype)), "bias_act")
+    return y
+
+
+def add_pair(residual: torch.Tensor, a: torch.Tensor, a_bias: Optional[torch.Tensor] = None,
+             b: Optional[torch.Tensor] = None, b_bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """residual += (a + a_bias) + (b + b_bias), in place and in float32: the outputs of two sublayers
+    that read the same input enter the stream together.  a, b float32 [T, H]; biases float32 [H] or None."""
+    _need(residual, "residual", torch.float32)
+    T, H = residual.shape
+    for t, n in ((a, "a"), (b, "b")):
+        if t is not None:
+            _need(t, n, torch.float32)
+            if t.shape != residual.shape:
+                raise KernelError(f"{n} {tuple(t.shape)} and residual {tuple(residual.shape)} differ")
+    for t, n in ((a_bias, "a_bias"), (b_bias, "b_bias")):
+        if t is not None:
+            _need(t, n, torch.float32)
+            if t.numel() != H:
+                raise KernelError(f"{n} has {t.numel()} elements, rows have {H}")
+    if b is None and b_bias is not None:
+        raise KernelError("a bias without its product")
+    lib = load_library("tokenwise")
+    _check(lib.tb_add_pair(_stream(), _ptr(residual), _ptr(a), _ptr(a_bias), _ptr(b), _ptr(b_bias), T, H), "add_pair")
+    return residual
+
+
 # ----------------------------------------------------------------------------- matrix products
 def streaming_row_limit(width: int) -> int:
     """The most rows of ``width`` elements that the streaming kernel takes (bfloat16): a batch of so many

@@ -1,0 +1,91 @@
+"""Entry points of ``csrc/sink_attention.cu``: windowed attention with kept first tokens, capped
+scores, a bias by distance and a softmax sink, for keys and values of different sizes.
+
+One pair of kernels serves both storage types (the 32-bit path and bfloat16 caches) and both kinds
+of step: a request's portion of a prompt and a single decoded token are rows of the same launch.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from tandem_b200.kernels import ops
+from tandem_b200.kernels.build import load_library
+
+
+def expand_distance_bias(table: torch.Tensor, bucket_of, max_distance: int) -> torch.Tensor:
+    """[buckets, heads] -> float32 [max_distance + 1, heads], one row per distance; the kernel clamps
+    larger distances to the last row, so ``bucket_of`` must be constant from ``max_distance`` on.
+    The buckets are computed on the host in double precision."""
+    index = torch.tensor([bucket_of(n) for n in range(max_distance + 1)], dtype=torch.int64, device=table.device)
+    return table.to(torch.float32)[index].contiguous()
+
+
+def prepare(qkv: torch.Tensor, bias: Optional[torch.Tensor], v_other: Optional[torch.Tensor], mix: Optional[torch.Tensor],
+            kv, num_heads: int, num_kv_heads: int, head_dim: int, value_dim: int, unit_norm: bool, eps: float) -> None:
+    """In place on the float32 projection ``qkv`` [T, nh dk + nkv dk + nkv dv]: biases added, q and k
+    heads divided by their root mean square (``unit_norm``); k and v stored at the tokens' cache slots,
+    v first mixed as (1 - mix) v + mix v_other where ``v_other`` (float32 rows of nkv dv values, any
+    row stride) is given.  Afterwards the q columns hold the queries and the v columns the layer's own
+    (unmixed) values."""
+    ops._need(qkv, "qkv", torch.float32)
+    T, cols = qkv.shape
+    if cols != (num_heads + num_kv_heads) * head_dim + num_kv_heads * value_dim:
+        raise ops.KernelError(f"qkv has {cols} columns, expected {(num_heads + num_kv_heads) * head_dim + num_kv_heads * value_dim}")
+    if bias is not None:
+        ops._need(bias, "bias", torch.float32)
+        if bias.numel() != cols:
+            raise ops.KernelError(f"bias has {bias.numel()} elements, qkv rows have {cols}")
+    stride_other = 0
+    if v_other is not None:
+        ops._need(v_other, "v_other", torch.float32, contiguous=False)
+        ops._need(mix, "mix", torch.float32)
+        if v_other.shape != (T, num_kv_heads * value_dim) or v_other.stride(1) != 1:
+            raise ops.KernelError(f"values to mix in have shape {tuple(v_other.shape)}, expected {(T, num_kv_heads * value_dim)}")
+        stride_other = v_other.stride(0)
+    if kv.writable:
+        ops._need(kv.slots, "slots", torch.int32)
+        if tuple(kv.k.shape[1:]) != (num_kv_heads, kv.page_size, head_dim) or \
+                tuple(kv.v.shape[1:]) != (num_kv_heads, kv.page_size, value_dim):
+            raise ops.KernelError(f"caches {tuple(kv.k.shape)} / {tuple(kv.v.shape)} do not fit {num_kv_heads} kv heads of "
+                                  f"{head_dim} / {value_dim}")
+    lib = load_library("sink_attention")
+    ops._check(lib.tb_sink_attention_prep(
+        ops._stream(), ops._ptr(qkv), qkv.stride(0), ops._ptr(bias), ops._ptr(v_other), stride_other, ops._ptr(mix),
+        ops._ptr(kv.slots), ops._ptr(kv.k), ops._ptr(kv.v), T, num_heads, num_kv_heads, head_dim, value_dim, kv.page_size,
+        int(bool(unit_norm)), ctypes.c_float(eps), int(bool(kv.writable)), ops._code(kv.k.dtype)), "sink_attention_prep")
+
+
+def attend(q: torch.Tensor, kv, ctx, num_heads: int, num_kv_heads: int, head_dim: int, value_dim: int,
+           window: Optional[int], keep_first: int, scale: float, softcap: Optional[float],
+           bias_by_distance: Optional[torch.Tensor], sink: Optional[torch.Tensor]) -> torch.Tensor:
+    """Attention output [T, nh dv] in the cache's type for the float32 queries in the first nh dk
+    columns of ``q``.  ``bias_by_distance`` float32 [distances, nh]; ``sink`` float32 [nh]."""
+    ops._need(q, "q", torch.float32, contiguous=False)
+    if q.stride(1) != 1 or q.shape[1] < num_heads * head_dim:
+        raise ops.KernelError("queries must be rows of at least nh dk contiguous float32 values")
+    if value_dim > 512:
+        raise ops.KernelError(f"value size {value_dim} is larger than the 512 this kernel takes")
+    T = q.shape[0]
+    max_dist = 0
+    if bias_by_distance is not None:
+        ops._need(bias_by_distance, "bias_by_distance", torch.float32)
+        if bias_by_distance.dim() != 2 or bias_by_distance.shape[1] != num_heads:
+            raise ops.KernelError(f"the distance bias has shape {tuple(bias_by_distance.shape)}, expected [distances, {num_heads}]")
+        max_dist = bias_by_distance.shape[0] - 1
+    if sink is not None:
+        ops._need(sink, "sink", torch.float32)
+        if sink.numel() != num_heads:
+            raise ops.KernelError(f"{sink.numel()} sinks for {num_heads} heads")
+    out = torch.empty((T, num_heads * value_dim), dtype=kv.k.dtype, device=q.device)
+    lib = load_library("sink_attention")
+    ops._check(lib.tb_sink_attention(
+        ops._stream(), ops._ptr(q), q.stride(0), ops._ptr(kv.k), ops._ptr(kv.v), ops._ptr(kv.block_table),
+        kv.block_table.stride(0), ops._ptr(ctx.seq_of_token), ops._ptr(ctx.positions), ops._ptr(out), T, num_heads,
+        num_kv_heads, head_dim, value_dim, kv.page_size, int(window or 0), int(keep_first if window else 0),
+        ctypes.c_float(scale), ctypes.c_float(softcap or 0.0), ops._ptr(bias_by_distance), max_dist, ops._ptr(sink),
+        ops._code(kv.k.dtype)), "sink_attention")
+    return out

@@ -1,10 +1,12 @@
 """The built-in parts, registered by kind."""
 
 from tandem_b200.parts.attention import PagedAttention
-from tandem_b200.parts.block import PreNormBlock
-from tandem_b200.parts.mlp import GatedMLP
+from tandem_b200.parts.block import ParallelBlock, PreNormBlock
+from tandem_b200.parts.mlp import DenseMLP, GatedMLP
 from tandem_b200.parts.norm import RMSNorm
+from tandem_b200.parts.recurrence import DecayRecurrence
 from tandem_b200.parts.rope import NoPosition, RotaryTable
+from tandem_b200.parts.sink_attention import SinkAttention
 from tandem_b200.registry import register_part
 
 register_part("mixer", "attention", PagedAttention)
@@ -13,3 +15,7 @@ register_part("norm", "rmsnorm", RMSNorm)
 register_part("position", "rope", RotaryTable)
 register_part("position", "none", NoPosition)
 register_part("block", "prenorm", PreNormBlock)
+register_part("mixer", "sink_attention", SinkAttention)
+register_part("mixer", "decay_recurrence", DecayRecurrence)
+register_part("feed_forward", "dense_mlp", DenseMLP)
+register_part("block", "parallel", ParallelBlock)

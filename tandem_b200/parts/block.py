@@ -4,6 +4,10 @@
 (x = the last sublayer's output, residual = the float32 stream) so that every "add, then
 normalise" is one kernel (12vivi/tandem python/tandem/models/llama_family.py:11-16,59-67).
 
+"parallel": n = norm(h); h <- h + (mixer(n) + feed_forward(n)): one norm, both sublayers read
+its output, and their outputs (with their biases) are added into the float32 stream together.
+The feed-forward may be absent.
+
 An arrangement declares the parts it works with as ``slots`` (slot name -> family; all needed)
 and ``optional_slots``; the decoder builds what the layer's spec lists under those names and
 hands the arrangement a layer whose attributes they are.  ``forward(layer, x, residual, ctx)``
@@ -52,3 +56,28 @@ class PreNormBlock:
         a = run(layer.mixer, h, ctx)
         h = normed(layer.feed_forward_norm, a, residual, ctx, layer.feed_forward)
         return run(layer.feed_forward, h, ctx)
+
+
+class ParallelBlock:
+    slots = {"norm": "norm", "mixer": "mixer"}
+    optional_slots = {"feed_forward": "feed_forward"}
+    takes_deferred = True
+
+    @staticmethod
+    def _terms(value, ctx: StepContext):
+        """(float32 tensor, bias or None) of a sublayer's output."""
+        if isinstance(value, deferred.Unsummed):
+            return value.product, value.bias
+        t = deferred.tensor(value)
+        return (t if t.dtype == torch.float32 else t.float()), None
+
+    def forward(self, layer, x, residual: torch.Tensor, ctx: StepContext):
+        from tandem_b200.kernels import ops
+
+        h = layer.norm.forward(deferred.tensor(x), residual, ctx.dtype)  # two readers: the norm is made whole
+        a, a_bias = self._terms(run(layer.mixer, h, ctx), ctx)
+        f, f_bias = (None, None)
+        if getattr(layer, "feed_forward", None) is not None:
+            f, f_bias = self._terms(run(layer.feed_forward, h, ctx), ctx)
+        ops.add_pair(residual, a, a_bias, f, f_bias)
+        return None  # everything is in the stream already

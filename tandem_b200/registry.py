@@ -1,6 +1,6 @@
 """Name -> implementation tables: architectures and the kinds of parts.
 
-One registry for whole architectures (``config.json``'s ``architectures[0]`` or ``model_type``
+One registry for whole architectures (``config.json``'s ``architectures[0]``, ``architecture`` or ``model_type``
 -> configuration class + plan builder), and one per kind of part (mixer, feed-forward, norm,
 position encoding, block arrangement).  Adding an architecture or a part is one ``register_*``
 call; the decoder, cache manager, step function and scheduler never name a model.
@@ -22,6 +22,8 @@ class Architecture:
     config_class: Any  # has from_dict(dict) and to_dict()
     build_plan: Callable[[Any], Any]  # config -> ModelPlan
     random_weights: Callable[..., Any]  # (config, seed, device, dtype) -> iterator of (name, tensor)
+    # (config, {tensor name: shape}) -> config: fills in sizes that only the checkpoint's tensors give
+    complete: Any = None
 
 
 _ARCHITECTURES: dict[str, Architecture] = {}
@@ -39,7 +41,7 @@ def resolve_architecture(config: dict) -> Architecture:
     """The architecture a config.json names; NotImplementedError lists the known ones otherwise
     (python/tandem/model_config.py:91-95)."""
     _load_builtin()
-    name = (config.get("architectures") or [None])[0]
+    name = (config.get("architectures") or [None])[0] or config.get("architecture")
     if name not in _ARCHITECTURES:
         name = _MODEL_TYPES.get(config.get("model_type", ""), name)
     if name not in _ARCHITECTURES:
@@ -78,5 +80,6 @@ def _load_builtin() -> None:
     if _loaded:
         return
     _loaded = True
+    import tandem_b200.models.fumanex  # noqa: F401
     import tandem_b200.models.qwen3  # noqa: F401
     import tandem_b200.parts  # noqa: F401

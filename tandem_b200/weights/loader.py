@@ -113,8 +113,11 @@ def check(params: dict[str, ParamSpec], have: dict[str, tuple], ignored: tuple, 
             if src.name not in have:
                 missing.append(src.name)
                 continue
-            rows = spec.shape[0] if src.rows is None else src.rows
-            wanted = (rows,) + tuple(spec.shape[1:])
+            if len(spec.shape) == 0:  # a single number
+                wanted = ()
+            else:
+                rows = spec.shape[0] if src.rows is None else src.rows
+                wanted = (rows,) + tuple(spec.shape[1:])
             if tuple(have[src.name]) != wanted:
                 wrong.append((src.name, have[src.name], wanted))
     patterns = [re.compile(p) for p in ignored]
