@@ -2,6 +2,7 @@
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--layers L] [--impl reference]
                     [--shape 8b|14b|32b] [--prompt-len P] [--new-tokens T] [--workload decode|mixed]
+                    [--design fumanex]
 
 The model has the layer sizes of Qwen3-8B with seeded random weights made on the device; prompts
 are seeded random token ids.  A step is one decode step of ``--batch`` requests whose prompts
@@ -17,6 +18,10 @@ of Qwen3-8B).  ``--workload mixed`` runs requests with prompts of random lengths
 tokens) through the scheduler with 128 greedy tokens each, prompt portions of up to 2,048 tokens
 beside decoded tokens, and prints its own line: generated and processed tokens per second of
 wall-clock time (benchmarks/bench_offline.py:64-86 of 12vivi/tandem).
+
+``--design fumanex`` prints a line of its own: prefill and decode throughput of Fumanex models with
+random weights at two sizes beside Qwen3 models of equal width, heads, layers and feed-forward
+weights, and the design's own kernels against their rooflines.  The default line is untouched.
 """
 
 from __future__ import annotations
@@ -298,6 +303,113 @@ def main_mixed(args, name: str, shape: dict) -> int:
     return 0
 
 
+# ---------------------------------------------------------------------------------------------
+# --design fumanex: the hybrid design beside Qwen3 at equal size
+def fumanex_shape(width: int, heads: int, kv_heads: int, ff: int, layers: int, window: int = 1024) -> dict:
+    """Layers of attention (window, kept first tokens, sink, bias by distance, mixed values), lightning and
+    retention in turn, head size 128 throughout; the dense feed-forward of two matrices has the weights of
+    the gated one of three that the Qwen3 model beside it has."""
+    att = dict(type="attention", mixer=dict(heads=heads, kv_heads=kv_heads, dim=128, vdim=128, scale=128 ** -0.5, softcap=30.0,
+                                            bias_max=window, v_mix=True, mask=dict(size=window, keep_first=4)), mlp=dict(kind="dense", ff=ff))
+    lig = dict(type="lightning", mixer=dict(heads=heads, dim=128, vdim=128, decay=[1.0 - 2.0 ** -(5 + 3 * i / heads) for i in range(heads)]),
+               mlp=dict(kind="dense", ff=ff))
+    ret = dict(type="retention", mixer=dict(heads=heads, dim=128, vdim=128, decay=[1.0 - 2.0 ** -(5 + 3 * i / heads) for i in range(heads)],
+                                            rot=dict(dims=64, base=1e6)), mlp=dict(kind="dense", ff=ff))
+    return dict(architecture="Fumanex", vocab=151936, width=width, embedding=dict(scale=1.0), logit_scale=1.0, norm=dict(eps=1e-6),
+                layers=[(att, lig, att, ret)[i % 4] for i in range(layers)])
+
+
+DESIGN_SIZES = {
+    "2k": (fumanex_shape(2048, 16, 4, 8256, 8), dict(QWEN3_8B, num_hidden_layers=8, hidden_size=2048, num_attention_heads=16,
+                                                    num_key_value_heads=4, intermediate_size=5504)),
+    "4k": (fumanex_shape(4096, 32, 8, 18432, 8), dict(QWEN3_8B, num_hidden_layers=8)),
+}
+
+
+def design_engine(config: dict, max_seqs: int, tokens_per_seq: int):
+    from tandem_b200 import EngineConfig, LLMEngine
+    from tandem_b200.engine.core import random_model
+
+    max_len = max(4096, -(-tokens_per_seq // PAGE) * PAGE)
+    if "max_position_embeddings" in config:
+        config = dict(config, max_position_embeddings=max_len)
+    decoder, cfg = random_model(config, seed=0, dtype="bfloat16")
+    return LLMEngine(EngineConfig(model="", dtype="bfloat16", block_size=PAGE, num_kv_blocks=max_seqs * (-(-tokens_per_seq // PAGE)) + 8,
+                                  max_num_seqs=max_seqs, max_num_batched_tokens=2048, max_model_len=max_len, cuda_graph=True,
+                                  cuda_graph_max_bs=max_seqs), decoder=decoder, model_config=cfg, load_tokenizer=False)
+
+
+def design_prefill_ms(eng, warmup: int, reps: int = 3) -> float:
+    import torch
+
+    from tandem_b200.engine.executor import StepEntry
+
+    toks = prompts(1, seed=99)[0]
+    times = []
+    for i in range(warmup + reps):
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        start.record()
+        eng.executor.step([StepEntry(f"p{i}", toks, [PROMPT - 1])], end=[f"p{i}"])
+        stop.record()
+        torch.cuda.synchronize()
+        if i >= warmup:
+            times.append(start.elapsed_time(stop))
+    return sorted(times)[len(times) // 2]
+
+
+def main_design(args) -> int:
+    import gc
+
+    import torch
+
+    from tandem_b200.kernels import microbench
+
+    pk = peaks()
+    sampler = ClockSampler()
+    sampler.start()
+    sizes = {}
+    launches = 0
+    for size, (fum, qwen) in DESIGN_SIZES.items():
+        row = {}
+        for name, config in (("fumanex", fum), ("qwen3", qwen)):
+            eng = design_engine(config, args.batch, PROMPT + NEW_TOKENS + args.steps + 2 * args.warmup + 32)
+            d = measure_decode(eng, args.batch, args.steps, args.warmup, PROMPT, NEW_TOKENS)
+            ms = design_prefill_ms(eng, args.warmup)
+            row[name] = {"prefill_tok_s": round(PROMPT * 1000.0 / ms, 1), "prefill_ms": round(ms, 3), "decode_tok_s": round(d["tok_s"], 1),
+                         "decode_ms_per_step": round(d["ms"], 4), "decode_e2e_tok_s": round(d["e2e_tok_s"], 1),
+                         "launches_per_decode_step": int(d["launches"]), "parameters": eng.decoder.num_parameters}
+            launches += int(d["launches"]) * args.steps
+            del eng, d
+            gc.collect()
+            torch.cuda.empty_cache()
+        sizes[size] = row
+    with torch.inference_mode():
+        att = microbench.sink_attention_case(PROMPT, args.batch, PROMPT, 32, 8, 128, 128, PAGE, 1024, 4, 20, True)
+        rec = microbench.recurrence_case(PROMPT, args.batch, 32, 128, 128, 20, True)
+    kernels = {
+        "sink_attention_tiles_prompt_2048": {"us": round(att["prefill_us"], 1), "tflops": round(att["prefill_tflops"], 1),
+                                             "frac_of_bf16_peak": round(att["prefill_tflops"] / pk["tflops"], 4)},
+        "sink_attention_decode_b%d" % args.batch: {"us": round(att["decode_us"], 1), "gbs": round(att["decode_gbs"], 1),
+                                                   "frac_of_hbm": round(att["decode_gbs"] / pk["hbm_gbs"], 4)},
+        "decay_recurrence_prompt_2048": {"us": round(rec["prefill_us"], 1), "tflops_fp32": round(rec["prefill_tflops"], 2)},
+        "decay_recurrence_decode_b%d" % args.batch: {"us": round(rec["decode_us"], 1), "gbs": round(rec["decode_gbs"], 1),
+                                                     "frac_of_hbm": round(rec["decode_gbs"] / pk["hbm_gbs"], 4)},
+    }
+    clocks = sampler.stop()
+    f4 = sizes["4k"]["fumanex"]
+    print(json.dumps({
+        "metric": f"decode tok/s at batch {args.batch}, Fumanex (8 layers, width 4096), {PROMPT:,}-token prompts (one B200)",
+        "value": f4["decode_tok_s"], "unit": "tok/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": f4["decode_ms_per_step"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic: seeded random weights and random token ids",
+        "config": {"model": "Fumanex beside Qwen3 at equal size", "global_batch": args.batch, "seq_len": PROMPT, "page_size": PAGE,
+                   "parallelism": "single GPU", "l2": "inputs larger than L2: each step streams every weight", "peaks": pk["source"]},
+        "e2e": {"value": f4["decode_e2e_tok_s"], "unit": "tok/s"}, "gpu_launches": launches,
+        "sizes": sizes, "kernels": kernels, "clocks": clocks}))
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -314,6 +426,7 @@ def main() -> int:
     ap.add_argument("--new-tokens", type=int, default=None)
     ap.add_argument("--workload", default="decode", choices=["decode", "mixed"])
     ap.add_argument("--policy", default="prefill_first", choices=["prefill_first", "decode_first"])
+    ap.add_argument("--design", default=None, choices=["fumanex"], help="another design beside Qwen3 at equal size (a line of its own)")
     args = ap.parse_args()
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not measured (use --gpus 1)")
@@ -324,6 +437,8 @@ def main() -> int:
         print(json.dumps(run_reference(args, SHAPES, prompts, ClockSampler)))
         return 0
     args.warmup = max(3, args.warmup)
+    if args.design == "fumanex":
+        return main_design(args)
     name, shape = SHAPES[args.shape]
     if args.layers is None:
         args.layers = shape["num_hidden_layers"]

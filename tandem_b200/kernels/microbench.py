@@ -7,6 +7,8 @@
     python -m tandem_b200.kernels.microbench norm-gemm --m 8 --n 6144 --k 4096
     python -m tandem_b200.kernels.microbench dispatch [--shapes 8b|14b|32b]
     python -m tandem_b200.kernels.microbench step-timeline --batch 8 --layers 4
+    python -m tandem_b200.kernels.microbench sink-attention --tokens 2048 --window 1024 --keep-first 4
+    python -m tandem_b200.kernels.microbench recurrence --tokens 2048 --heads 32 --head-dim 128
 
 Timing follows 12vivi/tandem's kernel benchmarks (benchmarks/bench_gemv.py:3-6,35-56): the calls are
 captured in one CUDA graph so that launch cost does not count, and weights or caches are rotated
@@ -251,6 +253,88 @@ def bench_prefill_attention(args) -> None:
           f"{flops / us / 1e6:7.1f} TFLOP/s")
 
 
+def sink_attention_case(tokens: int, batch: int, context: int, nh: int, nkv: int, dk: int, dv: int, ps: int, window: int,
+                        keep_first: int, iters: int, graph: bool) -> dict:
+    """The windowed attention with a sink: a prompt of ``tokens`` tokens on the tensor-core kernel, and a
+    decode step of ``batch`` requests at ``context`` tokens on the kernel of one warp per token and head."""
+    from tandem_b200.kernels import sink_attention as S
+    from tandem_b200.parts.base import KVView
+
+    class Ctx:
+        pass
+
+    scale, cap = dk ** -0.5, 30.0
+    bias = torch.randn(129, nh, device="cuda") * 0.1
+    sink = torch.randn(nh, device="cuda")
+    out = {}
+    # prompt
+    pages = -(-tokens // ps)
+    k = torch.randn(pages, nkv, ps, dk, device="cuda", dtype=torch.bfloat16)
+    v = torch.randn(pages, nkv, ps, dv, device="cuda", dtype=torch.bfloat16)
+    kv = KVView(k, v, torch.randperm(pages, device="cuda").to(torch.int32).view(1, pages), None, ps, True)
+    q = torch.randn(tokens, (nh + nkv) * dk + nkv * dv, device="cuda")
+    tiles = torch.tensor(S.plan_tiles([0], [tokens], nh // nkv), dtype=torch.int32, device="cuda")
+    us = time_calls(lambda i: S.attend_tiles(q, kv, tiles, nh, nkv, dk, dv, window, keep_first, scale, cap, bias, sink), iters, graph)
+    seen = sum(min(p + 1, window) + min(keep_first, max(0, p - window + 1)) for p in range(tokens)) if window else tokens * (tokens + 1) // 2
+    out["prefill_us"], out["prefill_tflops"] = us, 2.0 * nh * (dk + dv) * seen / us / 1e6
+    # decode
+    per_seq = -(-context // ps)
+    live = min(context, (window + keep_first) if window else context)
+    kv_bytes = batch * live * nkv * (dk + dv) * 2
+    copies = copies_for(batch * context * nkv * (dk + dv) * 2)
+    views = []
+    for _ in range(copies):
+        views.append(KVView(torch.randn(batch * per_seq, nkv, ps, dk, device="cuda", dtype=torch.bfloat16),
+                            torch.randn(batch * per_seq, nkv, ps, dv, device="cuda", dtype=torch.bfloat16),
+                            torch.randperm(batch * per_seq, device="cuda").to(torch.int32).view(batch, per_seq), None, ps, True))
+    ctx = Ctx()
+    ctx.positions = torch.full((batch,), context - 1, dtype=torch.int32, device="cuda")
+    ctx.seq_of_token = torch.arange(batch, dtype=torch.int32, device="cuda")
+    qd = torch.randn(batch, (nh + nkv) * dk + nkv * dv, device="cuda")
+    us = time_calls(lambda i: S.attend(qd, views[i % copies], ctx, nh, nkv, dk, dv, window, keep_first, scale, cap, bias, sink), iters, graph)
+    out["decode_us"], out["decode_gbs"] = us, kv_bytes / us / 1e3
+    return out
+
+
+def bench_sink_attention(args) -> None:
+    r = sink_attention_case(args.tokens, args.batch, args.context, args.heads, args.kv_heads, args.head_dim, args.value_dim or args.head_dim,
+                            args.page_size, args.window, args.keep_first, args.iters, args.graph)
+    print(f"sink attention heads={args.heads}/{args.kv_heads} dk={args.head_dim} dv={args.value_dim or args.head_dim} window={args.window}+{args.keep_first}: "
+          f"prompt of {args.tokens} tokens {r['prefill_us']:8.1f} us {r['prefill_tflops']:7.1f} TFLOP/s;  decode B={args.batch} context={args.context} "
+          f"{r['decode_us']:8.1f} us {r['decode_gbs']:7.0f} GB/s of visible keys and values")
+
+
+def recurrence_case(tokens: int, batch: int, H: int, dk: int, dv: int, iters: int, graph: bool) -> dict:
+    """The decay recurrence: one prompt of ``tokens`` tokens, and a decode step of ``batch`` requests (state read and written)."""
+    from tandem_b200.kernels import recurrence as R
+
+    decay = torch.full((H,), 0.99, device="cuda")
+    cols = 2 * H * dk + 2 * H * dv
+    out = {}
+    proj = torch.randn(tokens, cols, device="cuda") * 0.1
+    state = torch.zeros(2, H, dk, dv, device="cuda")
+    cu = torch.tensor([0, tokens], dtype=torch.int32, device="cuda")
+    slot = torch.zeros(1, dtype=torch.int32, device="cuda")
+    us = time_calls(lambda i: R.scan(proj, cu, slot, 1, state, decay, H, dk, dv), iters, graph)
+    out["prefill_us"], out["prefill_tflops"] = us, 4.0 * tokens * H * dk * dv / us / 1e6
+    state_bytes = batch * H * dk * dv * 4
+    copies = copies_for(state_bytes)
+    states = [torch.zeros(batch + 1, H, dk, dv, device="cuda") for _ in range(copies)]
+    projd = torch.randn(batch, cols, device="cuda") * 0.1
+    cud = torch.arange(batch + 1, dtype=torch.int32, device="cuda")
+    slots = torch.arange(batch, dtype=torch.int32, device="cuda")
+    us = time_calls(lambda i: R.scan(projd, cud, slots, batch, states[i % copies], decay, H, dk, dv), iters, graph)
+    out["decode_us"], out["decode_gbs"] = us, 2 * state_bytes / us / 1e3
+    return out
+
+
+def bench_recurrence(args) -> None:
+    r = recurrence_case(args.tokens, args.batch, args.heads, args.head_dim, args.value_dim or args.head_dim, args.iters, args.graph)
+    print(f"decay recurrence heads={args.heads} dk={args.head_dim} dv={args.value_dim or args.head_dim}: prompt of {args.tokens} tokens "
+          f"{r['prefill_us']:8.1f} us {r['prefill_tflops']:6.2f} TFLOP/s (4 T H dk dv);  decode B={args.batch} {r['decode_us']:8.1f} us "
+          f"{r['decode_gbs']:7.0f} GB/s of state read and written")
+
+
 def bench_tokenwise(args) -> None:
     from tandem_b200.kernels import ops
 
@@ -340,6 +424,15 @@ def main(argv=None) -> None:
     f.add_argument("--tokens", type=int, default=2048)
     f.add_argument("--start", type=int, default=0)
     f.set_defaults(fn=bench_prefill_attention)
+    for name, fn in (("sink-attention", bench_sink_attention), ("recurrence", bench_recurrence)):
+        c = sub.add_parser(name, parents=[common, shape])
+        c.add_argument("--tokens", type=int, default=2048)
+        c.add_argument("--batch", type=int, default=8)
+        c.add_argument("--context", type=int, default=2048)
+        c.add_argument("--value-dim", type=int, default=0)
+        c.add_argument("--window", type=int, default=1024)
+        c.add_argument("--keep-first", type=int, default=4)
+        c.set_defaults(fn=fn)
     t = sub.add_parser("tokenwise", parents=[common])
     t.add_argument("--tokens", type=int, default=2048)
     t.add_argument("--hidden", type=int, default=4096)

@@ -1,8 +1,12 @@
 """Entry points of ``csrc/sink_attention.cu``: windowed attention with kept first tokens, capped
 scores, a bias by distance and a softmax sink, for keys and values of different sizes.
 
-One pair of kernels serves both storage types (the 32-bit path and bfloat16 caches) and both kinds
-of step: a request's portion of a prompt and a single decoded token are rows of the same launch.
+``prepare`` + ``attend`` serve both storage types (the 32-bit path and bfloat16 caches) and any
+step: a request's portion of a prompt and a single decoded token are rows of the same launch, one
+warp per (token, head) on the CUDA cores.  In bfloat16, steps that bring prompt portions run
+``attend_tiles`` instead (``csrc/sink_attention_tile.cu``, compiled per key and value size): query
+tiles that the host cuts (``plan_tiles``), mma.sync tensor-core products, the same float32 score
+arithmetic.
 """
 
 from __future__ import annotations
@@ -14,6 +18,49 @@ import torch
 
 from tandem_b200.kernels import ops
 from tandem_b200.kernels.build import load_library
+
+
+TILE_ROWS = 64  # rows (token x query head of the group) of a query tile of the tensor-core kernel
+TILE_INTS = 4  # first token row, request, first position, number of tokens
+
+
+def tiles_apply(dtype: torch.dtype, head_dim: int, value_dim: int, groups: int, row_floats: int) -> bool:
+    """Whether the tensor-core kernel takes this shape: bfloat16 caches, key and value sizes that are
+    multiples of 16 up to 128, at most 64 query heads per kv head, query rows that start on 16 bytes."""
+    return (dtype == torch.bfloat16 and head_dim % 16 == 0 and value_dim % 16 == 0 and 16 <= head_dim <= 128
+            and 16 <= value_dim <= 128 and 1 <= groups <= TILE_ROWS and row_floats % 4 == 0
+            and ops.env("TANDEM_SINK_ATTENTION", "tiles") != "simt")
+
+
+def plan_tiles(host_starts, host_lens, groups: int) -> list:
+    """Query tiles for a step: every request's new tokens in runs of 64 // groups, those with the most
+    keys first; flat [first token row, request, first position, number of tokens] * n."""
+    per_tile = TILE_ROWS // groups
+    tiles, row = [], 0
+    for b, (start, n) in enumerate(zip(host_starts, host_lens)):
+        tiles.extend([row + off, b, start + off, min(per_tile, n - off)] for off in range(0, n, per_tile))
+        row += n
+    tiles.sort(key=lambda t: -(t[2] + t[3]))
+    return [x for t in tiles for x in t]
+
+
+def attend_tiles(q: torch.Tensor, kv, tiles: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int, value_dim: int,
+                 window: Optional[int], keep_first: int, scale: float, softcap: Optional[float],
+                 bias_by_distance: Optional[torch.Tensor], sink: Optional[torch.Tensor]) -> torch.Tensor:
+    """``attend`` for the tokens that ``tiles`` (int32 on the device, as ``plan_tiles`` cut them) name, on the tensor cores."""
+    ops._need(q, "q", torch.float32, contiguous=False)
+    ops._need(tiles, "tiles", torch.int32)
+    ops._need(kv.k, "k cache", torch.bfloat16)
+    T = q.shape[0]
+    max_dist = 0 if bias_by_distance is None else bias_by_distance.shape[0] - 1
+    out = torch.empty((T, num_heads * value_dim), dtype=torch.bfloat16, device=q.device)
+    lib = load_library("sink_attention_tile", (f"TB_DK={head_dim}", f"TB_DV={value_dim}"))
+    ops._check(lib.tb_sink_attention_tile(
+        ops._stream(), ops._ptr(q), q.stride(0), ops._ptr(kv.k), ops._ptr(kv.v), ops._ptr(kv.block_table),
+        kv.block_table.stride(0), ops._ptr(tiles), tiles.numel() // TILE_INTS, ops._ptr(out), num_heads, num_kv_heads,
+        kv.page_size, int(window or 0), int(keep_first if window else 0), ctypes.c_float(scale), ctypes.c_float(softcap or 0.0),
+        ops._ptr(bias_by_distance), max_dist, ops._ptr(sink)), "sink_attention_tile")
+    return out
 
 
 def expand_distance_bias(table: torch.Tensor, bucket_of, max_distance: int) -> torch.Tensor:

@@ -76,6 +76,23 @@ class SinkAttention(Mixer):
                                   f"got {b.max_distance}")
             self.bias_by_distance = kernels.expand_distance_bias(weights["rel"], b.bucket, b.max_distance)
 
+    def _tiles_key(self):
+        return ("sink_attention_tiles", self.spec.num_heads // self.spec.num_kv_heads)
+
+    def step_arrays(self, ctx: StepContext, out: dict) -> None:
+        """Steps that bring prompt portions run the tensor-core kernel where it takes the shape: its
+        query tiles are cut here, once per step for all layers with as many query heads per kv head."""
+        s, key = self.spec, self._tiles_key()
+        cols = (s.num_heads + s.num_kv_heads) * s.head_dim + s.num_kv_heads * s.value_dim
+        if key in out or ctx.max_new < 2 or \
+                not kernels.tiles_apply(ctx.dtype, s.head_dim, s.value_dim, s.num_heads // s.num_kv_heads, cols):
+            return
+        out[key] = kernels.plan_tiles(ctx.host_starts, ctx.host_lens, s.num_heads // s.num_kv_heads)
+
+    def step_array_capacity(self, bucket: int, max_model_len: int, page_size: int, out: dict) -> None:
+        """Steps of single tokens (the ones CUDA graphs capture) need no arrays: they run the kernel of one
+        warp per token and head, which reads the batch from the context's device arrays."""
+
     def forward(self, x, ctx: StepContext, defer: bool = False):
         s = self.spec
         x = deferred.tensor(x)
@@ -92,8 +109,14 @@ class SinkAttention(Mixer):
                     raise RuntimeError(f"values of {s.value_mix!r} are mixed in before the layer that makes them has run")
         kernels.prepare(qkv, self.qkv_bias, other, self.vmix if other is not None else None, kv, s.num_heads, s.num_kv_heads,
                         s.head_dim, s.value_dim, s.unit_norm, s.norm_eps)
-        o = kernels.attend(qkv, kv, ctx, s.num_heads, s.num_kv_heads, s.head_dim, s.value_dim, s.window, s.keep_first,
-                           s.scale, s.softcap, self.bias_by_distance, self.sink)
+        tiles = ctx.extras.get(self._tiles_key())
+        cols = qkv.shape[1]
+        if tiles is not None and kernels.tiles_apply(kv.k.dtype, s.head_dim, s.value_dim, s.num_heads // s.num_kv_heads, cols):
+            o = kernels.attend_tiles(qkv, kv, tiles, s.num_heads, s.num_kv_heads, s.head_dim, s.value_dim, s.window,
+                                     s.keep_first, s.scale, s.softcap, self.bias_by_distance, self.sink)
+        else:
+            o = kernels.attend(qkv, kv, ctx, s.num_heads, s.num_kv_heads, s.head_dim, s.value_dim, s.window, s.keep_first,
+                               s.scale, s.softcap, self.bias_by_distance, self.sink)
         y = ops.linear(o, self.o, out_dtype=torch.float32)
         if defer:
             return deferred.Unsummed(y, self.o_bias, ctx.dtype)

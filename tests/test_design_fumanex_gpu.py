@@ -46,7 +46,9 @@ def model_config(layers, width=48, vocab=211, embedding_scale=6.0, logit_scale=0
                 norm=dict(eps=eps), layers=layers)
 
 
-HYBRID = model_config([attention_layer(), lightning_layer(), attention_layer(), retention_layer(), lightning_layer(ff=None)])
+# the first two attention layers have sizes that the tensor-core kernel takes (bfloat16, steps with portions), the third has not
+HYBRID = model_config([attention_layer(vdim=32), lightning_layer(), attention_layer(vdim=32, window=70, keep_first=1), retention_layer(),
+                       attention_layer(dim=8, vdim=24, v_mix=False), lightning_layer(ff=None)])
 
 
 def make_folder(tmp_path, cfg, seed=3, edits=None, buckets=None, name="m") -> str:
@@ -126,6 +128,8 @@ def reference(folder, requests):
 ALONE = {
     "attention": [attention_layer(v_mix=False)],
     "attention_mixing": [attention_layer(ff=None), attention_layer(window=5, keep_first=0)],
+    "attention_tensor_cores": [attention_layer(heads=6, kv_heads=2, dim=32, vdim=16, window=9, keep_first=2, v_mix=False)],
+    "attention_tensor_cores_full": [attention_layer(heads=2, kv_heads=2, dim=64, vdim=64, window=None, v_mix=False, softcap=None)],
     "attention_full": [attention_layer(window=None, softcap=None, kv_heads=4, dim=24, vdim=24, v_mix=False)],
     "retention": [retention_layer()],
     "retention_whole_head_rotates": [retention_layer(dim=8, rot_dims=8, vdim=40)],
@@ -297,7 +301,7 @@ class FakeContext:
         self.positions, self.seq_of_token = positions, seq_of_token
 
 
-def attend_one_sequence(q, k, v, page_size, cuts, dtype, **options):
+def attend_one_sequence(q, k, v, page_size, cuts, dtype, tiles=False, **options):
     """The attention kernels alone: one sequence written to a paged cache (pages in scrambled order)
     portion by portion, every portion attending through the cache.  q [T, H, dk], k [T, G, dk], v [T, G, dv]."""
     from tandem_b200.kernels import sink_attention as kernels
@@ -318,8 +322,14 @@ def attend_one_sequence(q, k, v, page_size, cuts, dtype, **options):
         view = KVView(kc, vc, table, slots, page_size, True)
         kernels.prepare(qkv, None, None, None, view, H, G, dk, dv, False, 0.0)
         ctx = FakeContext(pos.cuda(), torch.zeros(n, dtype=torch.int32, device="cuda"))
-        out.append(kernels.attend(qkv, view, ctx, H, G, dk, dv, options.get("window"), options.get("keep_first", 0),
-                                  options.get("scale", 1.0), options.get("softcap"), options.get("bias"), options.get("sink")).float().cpu())
+        rest = (options.get("window"), options.get("keep_first", 0), options.get("scale", 1.0), options.get("softcap"),
+                options.get("bias"), options.get("sink"))
+        if tiles:
+            assert kernels.tiles_apply(dtype, dk, dv, H // G, qkv.shape[1])
+            plan = torch.tensor(kernels.plan_tiles([at], [n], H // G), dtype=torch.int32, device="cuda")
+            out.append(kernels.attend_tiles(qkv, view, plan, H, G, dk, dv, *rest).float().cpu())
+        else:
+            out.append(kernels.attend(qkv, view, ctx, H, G, dk, dv, *rest).float().cpu())
         at += n
     return torch.cat(out).view(T, H, dv)
 
@@ -341,6 +351,9 @@ def test_one_far_key_among_hundreds(dtype, dk, dv):
         for cuts in ([T], [512, 100] + [1] * 88, [37] * 18 + [34]):
             got = attend_one_sequence(q, k, v, 16, cuts, dtype, scale=0.5, **options).double()
             assert (got - ref).abs().max() < (1e-4 if dtype == torch.float32 else 3e-2), (options, cuts[:3])
+            if dtype == torch.bfloat16 and dk % 16 == 0 and dv % 16 == 0:
+                got = attend_one_sequence(q, k, v, 16, cuts, dtype, tiles=True, scale=0.5, **options).double()
+                assert (got - ref).abs().max() < 3e-2, ("tensor cores", options, cuts[:3])
     seen = plain.sink_softmax_attention(q, k, v, 0.5, None, None, 0, None, 0, None)
     hidden = plain.sink_softmax_attention(q, k, v, 0.5, None, None, 0, 64, 2, None)
     assert (seen[690] - hidden[690]).abs().max() > 0.1 and (seen[410] - hidden[410]).abs().max() > 0.1
@@ -360,6 +373,12 @@ def test_cap_bias_and_sink_in_the_kernel():
     assert (got - ref).abs().max() < 1e-4
     uncapped = plain.sink_softmax_attention(q, k, v, 0.4, None, rel, 50, 33, 4, sink)
     assert (uncapped - ref).abs().max() > 0.05
+    for page_size, cuts in ((8, [50, 2, 1, 1, 36]), (1, [90]), (32, [3] * 30)):  # the same on the tensor cores, from bfloat16 inputs
+        qb, kb, vb = (t.to(torch.bfloat16).double() for t in (q, k, v))
+        ref16 = plain.sink_softmax_attention(qb, kb, vb, 0.4, 5.0, rel, 50, 33, 4, sink)
+        got = attend_one_sequence(qb, kb, vb, page_size, cuts, torch.bfloat16, tiles=True, scale=0.4, softcap=5.0, window=33, keep_first=4,
+                                  bias=by_distance, sink=sink.float().cuda()).double()
+        assert (got - ref16).abs().max() < 3e-2, (page_size, cuts[:2])
 
 
 @pytest.mark.parametrize("dk,dv,H", [(32, 64, 4), (20, 8, 3), (96, 33, 1), (128, 128, 2)])
