@@ -10,9 +10,9 @@
 // `decay_recurrence_scan` walks each request's tokens in order from the state its slot holds and
 // leaves the new state there.  The columns of S are independent, so a block owns 32 of them for one
 // (request, head); warp w of the block holds rows [32 w, 32 w + 32) of those columns in registers.
-// Tokens are staged sixteen at a time in shared memory; per token a thread does 32 updates of its
-// state and 32 multiply-adds of its part of o, and the parts of the warps are summed in warp order
-// after the sixteen.  The order of operations for a token never depends on how the request was cut
+// Tokens are staged sixteen at a time in shared memory (two stages, the next one copied in while
+// this one is worked through); per token a thread does 32 updates of its state and 32 multiply-adds
+// of its part of o, and the parts of the warps are summed in warp order after the sixteen.  The order of operations for a token never depends on how the request was cut
 // into steps or on the batch, so the state and the output are the same bits under any schedule.
 // `decay_recurrence_post` divides o by a root mean square (per head without weight, or over all
 // heads with a weight), multiplies by a gate (SiLU or sigmoid of its own projection) and rounds to
@@ -58,19 +58,53 @@ __global__ void decay_recurrence_prep_kernel(float* __restrict__ proj, int strid
   }
 }
 
-// grid (ceil(dv / 32), H, requests); block = ceil(dk / 32) warps.
+__device__ __forceinline__ void dr_cp_async16(void* dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
+
+// Tokens [c0, c0 + n) of one head into a stage: q and k rows of dk floats (row pitch dkp), 32 value columns.
+// `vec`: every row piece starts on 16 bytes, so the copies are asynchronous 16-byte ones.
+__device__ __forceinline__ void dr_load_stage(const float* proj, int stride, int c0, int n, int q_col, int k_col, int v_col,
+                                              int v_cols, int dk, int dkp, float* q_s, float* k_s, float* v_s, bool vec) {
+  if (vec) {
+    const int per_row = dk >> 2;
+    for (int e = threadIdx.x; e < n * per_row; e += blockDim.x) {
+      const int c = e / per_row, d = (e % per_row) << 2;
+      const float* row = proj + (size_t)(c0 + c) * stride;
+      dr_cp_async16(q_s + c * dkp + d, row + q_col + d);
+      dr_cp_async16(k_s + c * dkp + d, row + k_col + d);
+    }
+    for (int e = threadIdx.x; e < n * 8; e += blockDim.x) {
+      const int c = e >> 3, l = (e & 7) << 2;
+      if (l < v_cols) dr_cp_async16(v_s + c * 32 + l, proj + (size_t)(c0 + c) * stride + v_col + l);
+    }
+  } else {
+    for (int e = threadIdx.x; e < n * dk; e += blockDim.x) {
+      const int c = e / dk, d = e % dk;
+      const float* row = proj + (size_t)(c0 + c) * stride;
+      q_s[c * dkp + d] = row[q_col + d];
+      k_s[c * dkp + d] = row[k_col + d];
+    }
+    for (int e = threadIdx.x; e < n * 32; e += blockDim.x) {
+      const int c = e >> 5, l = e & 31;
+      if (l < v_cols) v_s[e] = proj[(size_t)(c0 + c) * stride + v_col + l];
+    }
+  }
+  asm volatile("cp.async.commit_group;" ::: "memory");
+}
+
+// grid (ceil(dv / 32), H, requests); block = ceil(dk / 32) warps.  Two stages of sixteen tokens: the
+// next one is on its way while this one is worked through.
 __global__ void decay_recurrence_scan_kernel(const float* __restrict__ proj, int stride, const int* __restrict__ cu_seqlens,
                                              const int* __restrict__ state_slots, float* __restrict__ state,
                                              const float* __restrict__ decay, float* __restrict__ out, int H, int dk, int dv) {
-  extern __shared__ float smem[];
+  extern __shared__ __align__(16) float smem[];
   pdl_launch_dependents();
   pdl_wait();
   const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = blockDim.x >> 5;
   const int dkp = nw * 32;  // dk rounded up to whole warps
-  float* q_s = smem;                          // [DR_CHUNK][dkp]
-  float* k_s = q_s + DR_CHUNK * dkp;          // [DR_CHUNK][dkp]
-  float* v_s = k_s + DR_CHUNK * dkp;          // [DR_CHUNK][32]
-  float* part_s = v_s + DR_CHUNK * 32;        // [DR_CHUNK][nw][32]
+  const int stage_floats = 2 * DR_CHUNK * dkp + DR_CHUNK * 32;  // q, k, v of a stage
+  float* part_s = smem + 2 * stage_floats;                      // [DR_CHUNK][nw][32]
   const int h = blockIdx.y, b = blockIdx.z;
   const int j = blockIdx.x * 32 + lane;       // this thread's column of S
   const bool col_ok = j < dv;
@@ -84,31 +118,46 @@ __global__ void decay_recurrence_scan_kernel(const float* __restrict__ proj, int
     const int d = w * 32 + i;
     s[i] = (col_ok && d < dk) ? S[(size_t)d * dv + j] : 0.f;
   }
+  for (int e = threadIdx.x; e < 2 * stage_floats; e += blockDim.x) smem[e] = 0.f;  // rows beyond dk and columns beyond dv stay zero
+  __syncthreads();
   const int q_col = h * dk, k_col = H * dk + h * dk, v_col = 2 * H * dk + h * dv + blockIdx.x * 32;
-  for (int c0 = t0; c0 < t1; c0 += DR_CHUNK) {
+  const int v_cols = min(32, dv - blockIdx.x * 32);
+  const bool vec = ((dk | dv | stride) & 3) == 0 && (reinterpret_cast<uintptr_t>(proj) & 15) == 0;
+  dr_load_stage(proj, stride, t0, min(DR_CHUNK, t1 - t0), q_col, k_col, v_col, v_cols, dk, dkp, smem, smem + DR_CHUNK * dkp,
+                smem + 2 * DR_CHUNK * dkp, vec);
+  int slot = 0;
+  for (int c0 = t0; c0 < t1; c0 += DR_CHUNK, slot ^= 1) {
     const int n = min(DR_CHUNK, t1 - c0);
-    for (int e = threadIdx.x; e < n * dkp; e += blockDim.x) {
-      const int c = e / dkp, d = e % dkp;
-      const float* row = proj + (size_t)(c0 + c) * stride;
-      q_s[e] = d < dk ? row[q_col + d] : 0.f;
-      k_s[e] = d < dk ? row[k_col + d] : 0.f;
-    }
-    for (int e = threadIdx.x; e < n * 32; e += blockDim.x) {
-      const int c = e >> 5, l = e & 31;
-      v_s[e] = (blockIdx.x * 32 + l < dv) ? proj[(size_t)(c0 + c) * stride + v_col + l] : 0.f;
+    if (c0 + DR_CHUNK < t1) {
+      float* nxt = smem + (slot ^ 1) * stage_floats;
+      dr_load_stage(proj, stride, c0 + DR_CHUNK, min(DR_CHUNK, t1 - c0 - DR_CHUNK), q_col, k_col, v_col, v_cols, dk, dkp, nxt,
+                    nxt + DR_CHUNK * dkp, nxt + 2 * DR_CHUNK * dkp, vec);
+      asm volatile("cp.async.wait_group 1;" ::: "memory");
+    } else {
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
     }
     __syncthreads();
+    const float* q_s = smem + slot * stage_floats;
+    const float* k_s = q_s + DR_CHUNK * dkp;
+    const float* v_s = k_s + DR_CHUNK * dkp;
     for (int c = 0; c < n; ++c) {
       const float vj = v_s[c * 32 + lane];
-      const float* kc = k_s + c * dkp + w * 32;
-      const float* qc = q_s + c * dkp + w * 32;
-      float part = 0.f;
+      const float4* kc = reinterpret_cast<const float4*>(k_s + c * dkp + w * 32);
+      const float4* qc = reinterpret_cast<const float4*>(q_s + c * dkp + w * 32);
+      float part[4] = {0.f, 0.f, 0.f, 0.f};  // four chains: i mod 4; summed in a fixed order
 #pragma unroll
-      for (int i = 0; i < 32; ++i) {
-        s[i] = fmaf(kc[i], vj, g * s[i]);
-        part = fmaf(s[i], qc[i], part);
+      for (int i = 0; i < 8; ++i) {
+        const float4 k4 = kc[i], q4 = qc[i];
+        s[4 * i] = fmaf(k4.x, vj, g * s[4 * i]);
+        s[4 * i + 1] = fmaf(k4.y, vj, g * s[4 * i + 1]);
+        s[4 * i + 2] = fmaf(k4.z, vj, g * s[4 * i + 2]);
+        s[4 * i + 3] = fmaf(k4.w, vj, g * s[4 * i + 3]);
+        part[0] = fmaf(s[4 * i], q4.x, part[0]);
+        part[1] = fmaf(s[4 * i + 1], q4.y, part[1]);
+        part[2] = fmaf(s[4 * i + 2], q4.z, part[2]);
+        part[3] = fmaf(s[4 * i + 3], q4.w, part[3]);
       }
-      part_s[(c * nw + w) * 32 + lane] = part;
+      part_s[(c * nw + w) * 32 + lane] = (part[0] + part[1]) + (part[2] + part[3]);
     }
     __syncthreads();
     for (int c = w; c < n; c += nw) {  // the warps' parts in warp order
@@ -116,7 +165,7 @@ __global__ void decay_recurrence_scan_kernel(const float* __restrict__ proj, int
       for (int ww = 0; ww < nw; ++ww) o += part_s[(c * nw + ww) * 32 + lane];
       if (col_ok) out[(size_t)(c0 + c) * H * dv + h * dv + j] = o;
     }
-    __syncthreads();
+    // the next turn's loads go into the stage that was read two turns ago, and its parts are written behind its own barrier
   }
 #pragma unroll
   for (int i = 0; i < 32; ++i) {
@@ -183,7 +232,7 @@ int tb_decay_recurrence_scan(void* stream, const float* proj, int stride, const 
   if (requests <= 0) return 0;
   if (H <= 0 || dk <= 0 || dk > 1024 || dv <= 0 || H > 65535 || requests > 65535) return TB_ERR_BAD_SIZE;
   const int nw = (dk + 31) / 32;
-  const size_t smem = (size_t)(2 * tb::DR_CHUNK * nw * 32 + tb::DR_CHUNK * 32 + tb::DR_CHUNK * nw * 32) * sizeof(float);
+  const size_t smem = (size_t)(2 * (2 * tb::DR_CHUNK * nw * 32 + tb::DR_CHUNK * 32) + tb::DR_CHUNK * nw * 32) * sizeof(float);
   if (smem > 48 * 1024) {
     const cudaError_t e = cudaFuncSetAttribute(tb::decay_recurrence_scan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;

@@ -183,6 +183,216 @@ sink_attention_kernel(const float* __restrict__ q, int q_stride, const T* __rest
   }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Decode steps in bfloat16: the keys a token sees are cut into chunks of 128 by absolute position
+// (chunk c = keys [128 c, 128 c + 128)), chunk c goes to split c mod `splits`; a block of four warps
+// runs one (token, kv head, split) for all query heads of the group, so a key row is loaded once for
+// the group; a warp takes 32 keys of a chunk (lane = key for the scores, lane = value dims for the
+// output).  Every warp keeps the online-softmax state of its keys; the block merges its warps in warp
+// order and leaves one partial (maximum, sum, unnormalised output) per (token, head, split); the
+// merge kernel adds the splits in split order, the sink first.  Which keys meet in which partial
+// depends on the request's own positions only, so a token's result does not depend on the batch.
+constexpr int SD_WARPS = 4, SD_CHUNK = 128, SD_MAX_OWN = 8;  // value dims per lane: dv <= 256
+
+template <int GM, typename T>
+__global__ void __launch_bounds__(SD_WARPS * 32)
+sink_attention_split_kernel(const float* __restrict__ q, int q_stride, const T* __restrict__ k_cache, const T* __restrict__ v_cache,
+                            const int* __restrict__ block_table, int table_stride, const int* __restrict__ seq_of_token,
+                            const int* __restrict__ positions, float* __restrict__ part_o, float* __restrict__ part_ml, int nh,
+                            int nkv, int dk, int dv, int page_size, int window, int keep_first, float scale, float cap,
+                            const float* __restrict__ bias, int max_dist) {
+  extern __shared__ float smem[];  // GM * dk floats of queries, then SD_WARPS * GM * (2 + dv) floats for the merge
+  pdl_launch_dependents();
+  pdl_wait();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int split = blockIdx.x, splits = gridDim.x, kvh = blockIdx.y, t = blockIdx.z;
+  const int G = nh / nkv;
+  const int pos = positions[t];
+  const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+  const int kept = min(keep_first, lo);
+  const int* table = block_table + (size_t)seq_of_token[t] * table_stride;
+  float* q_s = smem;
+  float* merge_s = smem + GM * dk;
+  for (int i = threadIdx.x; i < G * dk; i += blockDim.x) q_s[i] = q[(size_t)t * q_stride + (size_t)kvh * G * dk + i];
+  __syncthreads();
+
+  float m[GM], l[GM], acc[GM][SD_MAX_OWN];
+#pragma unroll
+  for (int g = 0; g < GM; ++g) {
+    m[g] = -INFINITY;
+    l[g] = 0.f;
+#pragma unroll
+    for (int i = 0; i < SD_MAX_OWN; ++i) acc[g][i] = 0.f;
+  }
+  const float inv_cap = cap > 0.f ? 1.f / cap : 0.f;
+  const int last_chunk = pos / SD_CHUNK, first_window_chunk = lo / SD_CHUNK, kept_chunks = (kept + SD_CHUNK - 1) / SD_CHUNK;
+  for (int c = split; c <= last_chunk; c += splits) {
+    if (c >= kept_chunks && c < first_window_chunk) {  // between the kept tokens and the window: jump ahead, keeping c = split mod splits
+      c += (first_window_chunk - c) / splits * splits;
+      if (c < first_window_chunk) continue;
+    }
+    const int key = c * SD_CHUNK + warp * 32 + lane;
+    const bool seen = key <= pos && (key >= lo || key < kept);
+    long long tile = -1;
+    int r_in = 0;
+    float s[GM];
+#pragma unroll
+    for (int g = 0; g < GM; ++g) s[g] = -INFINITY;
+    if (seen) {
+      const int page = table[key / page_size];
+      if (page >= 0) {
+        tile = (long long)page * nkv + kvh;
+        r_in = key % page_size;
+        const T* kr = k_cache + tile * page_size * dk;
+        float dot[GM];
+#pragma unroll
+        for (int g = 0; g < GM; ++g) dot[g] = 0.f;
+        if (sizeof(T) == 2 && (dk & 7) == 0) {
+          for (int d = 0; d < dk; d += 8) {
+            const uint4 raw = *reinterpret_cast<const uint4*>(kr + cache_offset<T>(r_in, d, page_size, dk));
+            const __nv_bfloat162* hh = reinterpret_cast<const __nv_bfloat162*>(&raw);
+            float kf[8];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) { const float2 f = __bfloat1622float2(hh[i]); kf[2 * i] = f.x; kf[2 * i + 1] = f.y; }
+#pragma unroll
+            for (int g = 0; g < GM; ++g)
+              if (g < G) {
+                const float4 q0 = *reinterpret_cast<const float4*>(q_s + g * dk + d), q1 = *reinterpret_cast<const float4*>(q_s + g * dk + d + 4);
+                dot[g] = fmaf(q0.x, kf[0], dot[g]); dot[g] = fmaf(q0.y, kf[1], dot[g]); dot[g] = fmaf(q0.z, kf[2], dot[g]);
+                dot[g] = fmaf(q0.w, kf[3], dot[g]); dot[g] = fmaf(q1.x, kf[4], dot[g]); dot[g] = fmaf(q1.y, kf[5], dot[g]);
+                dot[g] = fmaf(q1.z, kf[6], dot[g]); dot[g] = fmaf(q1.w, kf[7], dot[g]);
+              }
+          }
+        } else {
+          for (int d = 0; d < dk; ++d) {
+            const float kf = to_float(kr[cache_offset<T>(r_in, d, page_size, dk)]);
+#pragma unroll
+            for (int g = 0; g < GM; ++g)
+              if (g < G) dot[g] = fmaf(q_s[g * dk + d], kf, dot[g]);
+          }
+        }
+#pragma unroll
+        for (int g = 0; g < GM; ++g)
+          if (g < G) {
+            float v = dot[g] * scale;
+            if (cap > 0.f) v = cap * tanhf(v * inv_cap);
+            if (bias) v += bias[(size_t)min(pos - key, max_dist) * nh + kvh * G + g];
+            s[g] = v;
+          }
+      }
+    }
+    float p[GM];
+#pragma unroll
+    for (int g = 0; g < GM; ++g) {
+      p[g] = 0.f;
+      if (g < G) {
+        const float m_new = fmaxf(m[g], warp_max(s[g]));
+        const float corr = (m[g] == -INFINITY) ? 0.f : expf(m[g] - m_new);
+        p[g] = (tile >= 0) ? expf(s[g] - m_new) : 0.f;
+        l[g] = l[g] * corr + warp_sum(p[g]);
+        m[g] = m_new;
+#pragma unroll
+        for (int i = 0; i < SD_MAX_OWN; ++i) acc[g][i] *= corr;
+      }
+    }
+    const unsigned live = __ballot_sync(0xffffffffu, tile >= 0);
+    const bool pairs = sizeof(T) == 2 && (dv & 63) == 0;  // a lane owns dims 2 lane + 64 i and the next one: 4-byte loads
+    for (int j = 0; j < 32; ++j) {
+      if (!((live >> j) & 1u)) continue;
+      const long long tj = __shfl_sync(0xffffffffu, tile, j);
+      const int rin = __shfl_sync(0xffffffffu, r_in, j);
+      const T* vr = v_cache + tj * page_size * dv;
+      float pj[GM];
+#pragma unroll
+      for (int g = 0; g < GM; ++g) pj[g] = __shfl_sync(0xffffffffu, p[g], j);
+      if (pairs) {
+#pragma unroll
+        for (int i = 0; i < SD_MAX_OWN / 2; ++i) {
+          const int d = 2 * lane + 64 * i;
+          if (d < dv) {
+            const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(vr + cache_offset<T>(rin, d, page_size, dv)));
+#pragma unroll
+            for (int g = 0; g < GM; ++g)
+              if (g < G) { acc[g][2 * i] = fmaf(pj[g], f.x, acc[g][2 * i]); acc[g][2 * i + 1] = fmaf(pj[g], f.y, acc[g][2 * i + 1]); }
+          }
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < SD_MAX_OWN; ++i) {
+          const int d = lane + 32 * i;
+          if (d < dv) {
+            const float f = to_float(vr[cache_offset<T>(rin, d, page_size, dv)]);
+#pragma unroll
+            for (int g = 0; g < GM; ++g)
+              if (g < G) acc[g][i] = fmaf(pj[g], f, acc[g][i]);
+          }
+        }
+      }
+    }
+  }
+  // the block's warps in warp order: [warp][g][2 + dv]
+  const bool pairs = sizeof(T) == 2 && (dv & 63) == 0;
+  const int rec = 2 + dv;
+#pragma unroll
+  for (int g = 0; g < GM; ++g)
+    if (g < G) {
+      float* dst = merge_s + ((size_t)warp * GM + g) * rec;
+      if (lane == 0) { dst[0] = m[g]; dst[1] = l[g]; }
+#pragma unroll
+      for (int i = 0; i < SD_MAX_OWN; ++i) {
+        const int d = pairs ? 2 * lane + 64 * (i >> 1) + (i & 1) : lane + 32 * i;
+        if (d < dv) dst[2 + d] = acc[g][i];
+      }
+    }
+  __syncthreads();
+  for (int g = warp; g < G; g += SD_WARPS) {  // warp w merges heads w, w + 4, ...
+    float mm = -INFINITY;
+    for (int w = 0; w < SD_WARPS; ++w) mm = fmaxf(mm, merge_s[((size_t)w * GM + g) * rec]);
+    float ll = 0.f;
+    float f[SD_WARPS];
+    for (int w = 0; w < SD_WARPS; ++w) {
+      const float mw = merge_s[((size_t)w * GM + g) * rec];
+      f[w] = mw == -INFINITY ? 0.f : expf(mw - mm);
+      ll += merge_s[((size_t)w * GM + g) * rec + 1] * f[w];
+    }
+    const size_t row = ((size_t)t * nh + kvh * G + g) * splits + split;
+    if (lane == 0) { part_ml[2 * row] = mm; part_ml[2 * row + 1] = ll; }
+    for (int d = lane; d < dv; d += 32) {
+      float o = 0.f;
+      for (int w = 0; w < SD_WARPS; ++w) o += merge_s[((size_t)w * GM + g) * rec + 2 + d] * f[w];
+      part_o[row * dv + d] = o;
+    }
+  }
+}
+
+// One warp per (token, head): the sink, then the splits in order.
+template <typename T>
+__global__ void sink_attention_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                            const float* __restrict__ sink, T* __restrict__ out, int rows, int nh, int dv, int splits) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int lane = threadIdx.x & 31;
+  const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const int h = row % nh;
+  float mm = sink ? sink[h] : -INFINITY;
+  for (int s = 0; s < splits; ++s) mm = fmaxf(mm, part_ml[2 * ((size_t)row * splits + s)]);
+  float ll = sink ? expf(sink[h] - mm) : 0.f;
+  float f = 0.f;  // lane s keeps the factor of split s (splits <= 32)
+  for (int s = 0; s < splits; ++s) {
+    const float ms = part_ml[2 * ((size_t)row * splits + s)];
+    const float fs = ms == -INFINITY ? 0.f : expf(ms - mm);
+    ll += part_ml[2 * ((size_t)row * splits + s) + 1] * fs;
+    if (lane == s) f = fs;
+  }
+  const float inv = ll > 0.f ? 1.f / ll : 0.f;
+  for (int d = lane; d < dv; d += 32) {
+    float o = 0.f;
+    for (int s = 0; s < splits; ++s) o += part_o[((size_t)row * splits + s) * dv + d] * __shfl_sync(0xffffffffu, f, s);
+    out[(size_t)row * dv + d] = from_float<T>(o * inv);
+  }
+}
+
 }  // namespace tb
 
 extern "C" {
@@ -217,6 +427,39 @@ int tb_sink_attention(void* stream, const float* q, int q_stride, const void* k_
                                       (const T*)k_cache, (const T*)v_cache, block_table, table_stride, seq_of_token, positions,
                                       (T*)out, T_tokens, nh, nkv, dk, dv, page_size, window, keep_first, scale, cap, bias, max_dist,
                                       sink));
+}
+
+// The same attention for steps of single tokens, cut over `splits` blocks per (token, kv head):
+// part_o float32 [T nh splits dv], part_ml float32 [T nh splits 2] are scratch.
+int tb_sink_attention_split(void* stream, const float* q, int q_stride, const void* k_cache, const void* v_cache,
+                            const int* block_table, int table_stride, const int* seq_of_token, const int* positions, void* out,
+                            float* part_o, float* part_ml, int splits, int T_tokens, int nh, int nkv, int dk, int dv, int page_size,
+                            int window, int keep_first, float scale, float cap, const float* bias, int max_dist, const float* sink,
+                            int dtype) {
+  if (T_tokens <= 0) return 0;
+  if (dk <= 0 || dv <= 0 || dv > 32 * tb::SD_MAX_OWN || (dk & 3) || nkv <= 0 || nh % nkv != 0 || nh / nkv > 8 || page_size <= 0 ||
+      window < 0 || keep_first < 0 || splits <= 0 || splits > 32 || T_tokens > 65535 || nkv > 65535 || (q_stride & 3) || (bias && max_dist < 0))
+    return TB_ERR_BAD_SIZE;
+  const int G = nh / nkv, GM = G <= 1 ? 1 : G <= 2 ? 2 : G <= 4 ? 4 : 8;
+  const size_t smem = (size_t)(GM * dk + tb::SD_WARPS * GM * (2 + dv)) * sizeof(float);
+  if (smem > 48 * 1024) return TB_ERR_BAD_SIZE;
+  const dim3 grid(splits, nkv, T_tokens), block(tb::SD_WARPS * 32);
+  int rc = TB_ERR_BAD_DTYPE;
+#define TB_SPLIT(GMV, TT)                                                                                                       \
+  rc = tb::launch(tb::sink_attention_split_kernel<GMV, TT>, grid, block, smem, stream, q, q_stride, (const TT*)k_cache,          \
+                  (const TT*)v_cache, block_table, table_stride, seq_of_token, positions, part_o, part_ml, nh, nkv, dk, dv,      \
+                  page_size, window, window > 0 ? keep_first : 0, scale, cap, bias, max_dist)
+  if (dtype == TB_BF16) {
+    using B = __nv_bfloat16;
+    if (GM == 1) TB_SPLIT(1, B); else if (GM == 2) TB_SPLIT(2, B); else if (GM == 4) TB_SPLIT(4, B); else TB_SPLIT(8, B);
+  } else if (dtype == TB_F32) {
+    if (GM == 1) TB_SPLIT(1, float); else if (GM == 2) TB_SPLIT(2, float); else if (GM == 4) TB_SPLIT(4, float); else TB_SPLIT(8, float);
+  }
+#undef TB_SPLIT
+  if (rc != 0) return rc;
+  const int rows = T_tokens * nh;
+  TB_DISPATCH_DTYPE(dtype, tb::launch(tb::sink_attention_merge_kernel<T>, dim3((rows + 3) / 4), dim3(128), 0, stream, part_o, part_ml,
+                                      sink, (T*)out, rows, nh, dv, splits));
 }
 
 }  // extern "C"

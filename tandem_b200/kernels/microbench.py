@@ -291,7 +291,8 @@ def sink_attention_case(tokens: int, batch: int, context: int, nh: int, nkv: int
     ctx.positions = torch.full((batch,), context - 1, dtype=torch.int32, device="cuda")
     ctx.seq_of_token = torch.arange(batch, dtype=torch.int32, device="cuda")
     qd = torch.randn(batch, (nh + nkv) * dk + nkv * dv, device="cuda")
-    us = time_calls(lambda i: S.attend(qd, views[i % copies], ctx, nh, nkv, dk, dv, window, keep_first, scale, cap, bias, sink), iters, graph)
+    decode = S.attend_split if S.split_applies(torch.bfloat16, dk, dv, nh // nkv, qd.shape[1]) else S.attend
+    us = time_calls(lambda i: decode(qd, views[i % copies], ctx, nh, nkv, dk, dv, window, keep_first, scale, cap, bias, sink), iters, graph)
     out["decode_us"], out["decode_gbs"] = us, kv_bytes / us / 1e3
     return out
 

@@ -63,6 +63,48 @@ def attend_tiles(q: torch.Tensor, kv, tiles: torch.Tensor, num_heads: int, num_k
     return out
 
 
+SPLIT_CHUNK = 128  # keys per chunk of the split kernel
+MAX_SPLITS = 16
+
+
+def split_applies(dtype: torch.dtype, head_dim: int, value_dim: int, groups: int, row_floats: int) -> bool:
+    """Whether steps of single tokens run the kernel that cuts a token's keys over several blocks:
+    bfloat16 caches (the 32-bit path keeps the kernel whose sums never depend on the cut), up to eight
+    query heads per kv head, values of up to 256."""
+    smem = (max(1, groups) * head_dim + 4 * 8 * (2 + value_dim)) * 4
+    return (dtype == torch.bfloat16 and 1 <= groups <= 8 and value_dim <= 256 and head_dim % 4 == 0 and row_floats % 4 == 0
+            and smem <= 48 * 1024 and ops.env("TANDEM_SINK_ATTENTION", "tiles") != "simt")
+
+
+def num_splits(window: Optional[int], keep_first: int) -> int:
+    """Blocks per (token, kv head): the chunks a window (with its kept first tokens) can touch, sixteen at most."""
+    if not window:
+        return MAX_SPLITS
+    return max(1, min(MAX_SPLITS, -(-(window + keep_first) // SPLIT_CHUNK) + 1))
+
+
+def attend_split(q: torch.Tensor, kv, ctx, num_heads: int, num_kv_heads: int, head_dim: int, value_dim: int,
+                 window: Optional[int], keep_first: int, scale: float, softcap: Optional[float],
+                 bias_by_distance: Optional[torch.Tensor], sink: Optional[torch.Tensor]) -> torch.Tensor:
+    """``attend`` for steps of single tokens, each token's keys cut over several blocks and merged in a fixed order."""
+    ops._need(q, "q", torch.float32, contiguous=False)
+    T = q.shape[0]
+    max_dist = 0 if bias_by_distance is None else bias_by_distance.shape[0] - 1
+    splits = num_splits(window, keep_first)
+    out = torch.empty((T, num_heads * value_dim), dtype=kv.k.dtype, device=q.device)
+    part_o = torch.empty((T * num_heads * splits, value_dim), dtype=torch.float32, device=q.device)
+    part_ml = torch.empty((T * num_heads * splits, 2), dtype=torch.float32, device=q.device)
+    lib = load_library("sink_attention")
+    ops._check(lib.tb_sink_attention_split(
+        ops._stream(), ops._ptr(q), q.stride(0), ops._ptr(kv.k), ops._ptr(kv.v), ops._ptr(kv.block_table),
+        kv.block_table.stride(0), ops._ptr(ctx.seq_of_token), ops._ptr(ctx.positions), ops._ptr(out), ops._ptr(part_o),
+        ops._ptr(part_ml), splits, T, num_heads, num_kv_heads, head_dim, value_dim, kv.page_size, int(window or 0),
+        int(keep_first if window else 0), ctypes.c_float(scale), ctypes.c_float(softcap or 0.0), ops._ptr(bias_by_distance),
+        max_dist, ops._ptr(sink), ops._code(kv.k.dtype)), "sink_attention_split")
+    ops.launches += 1  # two kernels
+    return out
+
+
 def expand_distance_bias(table: torch.Tensor, bucket_of, max_distance: int) -> torch.Tensor:
     """[buckets, heads] -> float32 [max_distance + 1, heads], one row per distance; the kernel clamps
     larger distances to the last row, so ``bucket_of`` must be constant from ``max_distance`` on.

@@ -114,6 +114,9 @@ class SinkAttention(Mixer):
         if tiles is not None and kernels.tiles_apply(kv.k.dtype, s.head_dim, s.value_dim, s.num_heads // s.num_kv_heads, cols):
             o = kernels.attend_tiles(qkv, kv, tiles, s.num_heads, s.num_kv_heads, s.head_dim, s.value_dim, s.window,
                                      s.keep_first, s.scale, s.softcap, self.bias_by_distance, self.sink)
+        elif ctx.max_new == 1 and kernels.split_applies(kv.k.dtype, s.head_dim, s.value_dim, s.num_heads // s.num_kv_heads, cols):
+            o = kernels.attend_split(qkv, kv, ctx, s.num_heads, s.num_kv_heads, s.head_dim, s.value_dim, s.window, s.keep_first,
+                                     s.scale, s.softcap, self.bias_by_distance, self.sink)
         else:
             o = kernels.attend(qkv, kv, ctx, s.num_heads, s.num_kv_heads, s.head_dim, s.value_dim, s.window, s.keep_first,
                                s.scale, s.softcap, self.bias_by_distance, self.sink)

@@ -324,7 +324,9 @@ def attend_one_sequence(q, k, v, page_size, cuts, dtype, tiles=False, **options)
         ctx = FakeContext(pos.cuda(), torch.zeros(n, dtype=torch.int32, device="cuda"))
         rest = (options.get("window"), options.get("keep_first", 0), options.get("scale", 1.0), options.get("softcap"),
                 options.get("bias"), options.get("sink"))
-        if tiles:
+        if tiles and n == 1 and kernels.split_applies(dtype, dk, dv, H // G, qkv.shape[1]):  # single tokens: the split kernel
+            out.append(kernels.attend_split(qkv, view, ctx, H, G, dk, dv, *rest).float().cpu())
+        elif tiles:
             assert kernels.tiles_apply(dtype, dk, dv, H // G, qkv.shape[1])
             plan = torch.tensor(kernels.plan_tiles([at], [n], H // G), dtype=torch.int32, device="cuda")
             out.append(kernels.attend_tiles(qkv, view, plan, H, G, dk, dv, *rest).float().cpu())
