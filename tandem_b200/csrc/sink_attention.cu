@@ -248,20 +248,29 @@ sink_attention_split_kernel(const float* __restrict__ q, int q_stride, const T* 
 #pragma unroll
         for (int g = 0; g < GM; ++g) dot[g] = 0.f;
         if (sizeof(T) == 2 && (dk & 7) == 0) {
-          for (int d = 0; d < dk; d += 8) {
-            const uint4 raw = *reinterpret_cast<const uint4*>(kr + cache_offset<T>(r_in, d, page_size, dk));
-            const __nv_bfloat162* hh = reinterpret_cast<const __nv_bfloat162*>(&raw);
-            float kf[8];
+          for (int d0 = 0; d0 < dk; d0 += 32) {  // four 16-byte loads are issued before the first is used
+            uint4 raw[4];
 #pragma unroll
-            for (int i = 0; i < 4; ++i) { const float2 f = __bfloat1622float2(hh[i]); kf[2 * i] = f.x; kf[2 * i + 1] = f.y; }
+            for (int u = 0; u < 4; ++u)
+              raw[u] = d0 + 8 * u < dk ? *reinterpret_cast<const uint4*>(kr + cache_offset<T>(r_in, d0 + 8 * u, page_size, dk))
+                                       : make_uint4(0, 0, 0, 0);
 #pragma unroll
-            for (int g = 0; g < GM; ++g)
-              if (g < G) {
-                const float4 q0 = *reinterpret_cast<const float4*>(q_s + g * dk + d), q1 = *reinterpret_cast<const float4*>(q_s + g * dk + d + 4);
-                dot[g] = fmaf(q0.x, kf[0], dot[g]); dot[g] = fmaf(q0.y, kf[1], dot[g]); dot[g] = fmaf(q0.z, kf[2], dot[g]);
-                dot[g] = fmaf(q0.w, kf[3], dot[g]); dot[g] = fmaf(q1.x, kf[4], dot[g]); dot[g] = fmaf(q1.y, kf[5], dot[g]);
-                dot[g] = fmaf(q1.z, kf[6], dot[g]); dot[g] = fmaf(q1.w, kf[7], dot[g]);
-              }
+            for (int u = 0; u < 4; ++u) {
+              const int d = d0 + 8 * u;
+              if (d >= dk) break;
+              const __nv_bfloat162* hh = reinterpret_cast<const __nv_bfloat162*>(&raw[u]);
+              float kf[8];
+#pragma unroll
+              for (int i = 0; i < 4; ++i) { const float2 f = __bfloat1622float2(hh[i]); kf[2 * i] = f.x; kf[2 * i + 1] = f.y; }
+#pragma unroll
+              for (int g = 0; g < GM; ++g)
+                if (g < G) {
+                  const float4 q0 = *reinterpret_cast<const float4*>(q_s + g * dk + d), q1 = *reinterpret_cast<const float4*>(q_s + g * dk + d + 4);
+                  dot[g] = fmaf(q0.x, kf[0], dot[g]); dot[g] = fmaf(q0.y, kf[1], dot[g]); dot[g] = fmaf(q0.z, kf[2], dot[g]);
+                  dot[g] = fmaf(q0.w, kf[3], dot[g]); dot[g] = fmaf(q1.x, kf[4], dot[g]); dot[g] = fmaf(q1.y, kf[5], dot[g]);
+                  dot[g] = fmaf(q1.z, kf[6], dot[g]); dot[g] = fmaf(q1.w, kf[7], dot[g]);
+                }
+            }
           }
         } else {
           for (int d = 0; d < dk; ++d) {
@@ -297,35 +306,60 @@ sink_attention_split_kernel(const float* __restrict__ q, int q_stride, const T* 
     }
     const unsigned live = __ballot_sync(0xffffffffu, tile >= 0);
     const bool pairs = sizeof(T) == 2 && (dv & 63) == 0;  // a lane owns dims 2 lane + 64 i and the next one: 4-byte loads
+    if (live == 0u) continue;
+    // keys that are not seen have weight zero and read row 0 of the cache's first tile (always there): no branch in
+    // the loop, so that the loads of eight keys are on their way together
+    if (pairs) {
+      for (int j0 = 0; j0 < 32; j0 += 8) {
+        if (!((live >> j0) & 0xffu)) continue;
+        __nv_bfloat162 vv[8][SD_MAX_OWN / 2];
+#pragma unroll
+        for (int jj = 0; jj < 8; ++jj) {  // the loads of eight keys first
+          const long long tj = __shfl_sync(0xffffffffu, tile, j0 + jj);
+          const int rin = __shfl_sync(0xffffffffu, r_in, j0 + jj);
+          const T* vr = v_cache + (tj < 0 ? 0 : tj) * page_size * dv;
+          const int rr = tj < 0 ? 0 : rin;
+#pragma unroll
+          for (int i = 0; i < SD_MAX_OWN / 2; ++i) {
+            const int d = 2 * lane + 64 * i;
+            if (d < dv) vv[jj][i] = *reinterpret_cast<const __nv_bfloat162*>(vr + cache_offset<T>(rr, d, page_size, dv));
+          }
+        }
+#pragma unroll
+        for (int jj = 0; jj < 8; ++jj) {
+          float pj[GM];
+#pragma unroll
+          for (int g = 0; g < GM; ++g) pj[g] = __shfl_sync(0xffffffffu, p[g], j0 + jj);
+#pragma unroll
+          for (int i = 0; i < SD_MAX_OWN / 2; ++i) {
+            if (2 * lane + 64 * i < dv) {
+              const float2 f = __bfloat1622float2(vv[jj][i]);
+#pragma unroll
+              for (int g = 0; g < GM; ++g)
+                if (g < G) { acc[g][2 * i] = fmaf(pj[g], f.x, acc[g][2 * i]); acc[g][2 * i + 1] = fmaf(pj[g], f.y, acc[g][2 * i + 1]); }
+            }
+          }
+        }
+      }
+      continue;
+    }
+#pragma unroll 4
     for (int j = 0; j < 32; ++j) {
-      if (!((live >> j) & 1u)) continue;
       const long long tj = __shfl_sync(0xffffffffu, tile, j);
       const int rin = __shfl_sync(0xffffffffu, r_in, j);
-      const T* vr = v_cache + tj * page_size * dv;
+      const T* vr = v_cache + (tj < 0 ? 0 : tj) * page_size * dv;
+      const int rr = tj < 0 ? 0 : rin;
       float pj[GM];
 #pragma unroll
       for (int g = 0; g < GM; ++g) pj[g] = __shfl_sync(0xffffffffu, p[g], j);
-      if (pairs) {
 #pragma unroll
-        for (int i = 0; i < SD_MAX_OWN / 2; ++i) {
-          const int d = 2 * lane + 64 * i;
-          if (d < dv) {
-            const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(vr + cache_offset<T>(rin, d, page_size, dv)));
+      for (int i = 0; i < SD_MAX_OWN; ++i) {
+        const int d = lane + 32 * i;
+        if (d < dv) {
+          const float f = to_float(vr[cache_offset<T>(rr, d, page_size, dv)]);
 #pragma unroll
-            for (int g = 0; g < GM; ++g)
-              if (g < G) { acc[g][2 * i] = fmaf(pj[g], f.x, acc[g][2 * i]); acc[g][2 * i + 1] = fmaf(pj[g], f.y, acc[g][2 * i + 1]); }
-          }
-        }
-      } else {
-#pragma unroll
-        for (int i = 0; i < SD_MAX_OWN; ++i) {
-          const int d = lane + 32 * i;
-          if (d < dv) {
-            const float f = to_float(vr[cache_offset<T>(rin, d, page_size, dv)]);
-#pragma unroll
-            for (int g = 0; g < GM; ++g)
-              if (g < G) acc[g][i] = fmaf(pj[g], f, acc[g][i]);
-          }
+          for (int g = 0; g < GM; ++g)
+            if (g < G) acc[g][i] = fmaf(pj[g], f, acc[g][i]);
         }
       }
     }
@@ -375,19 +409,16 @@ __global__ void sink_attention_merge_kernel(const float* __restrict__ part_o, co
   const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (row >= rows) return;
   const int h = row % nh;
-  float mm = sink ? sink[h] : -INFINITY;
-  for (int s = 0; s < splits; ++s) mm = fmaxf(mm, part_ml[2 * ((size_t)row * splits + s)]);
-  float ll = sink ? expf(sink[h] - mm) : 0.f;
-  float f = 0.f;  // lane s keeps the factor of split s (splits <= 32)
-  for (int s = 0; s < splits; ++s) {
-    const float ms = part_ml[2 * ((size_t)row * splits + s)];
-    const float fs = ms == -INFINITY ? 0.f : expf(ms - mm);
-    ll += part_ml[2 * ((size_t)row * splits + s) + 1] * fs;
-    if (lane == s) f = fs;
-  }
+  // lane s reads the statistics of split s (splits <= 32): one round of loads, sums by the warp's fixed butterfly
+  const float ms = lane < splits ? part_ml[2 * ((size_t)row * splits + lane)] : -INFINITY;
+  const float ls = lane < splits ? part_ml[2 * ((size_t)row * splits + lane) + 1] : 0.f;
+  const float mm = fmaxf(sink ? sink[h] : -INFINITY, warp_max(ms));
+  const float f = ms == -INFINITY ? 0.f : expf(ms - mm);
+  const float ll = warp_sum(ls * f) + (sink ? expf(sink[h] - mm) : 0.f);
   const float inv = ll > 0.f ? 1.f / ll : 0.f;
   for (int d = lane; d < dv; d += 32) {
     float o = 0.f;
+#pragma unroll 8
     for (int s = 0; s < splits; ++s) o += part_o[((size_t)row * splits + s) * dv + d] * __shfl_sync(0xffffffffu, f, s);
     out[(size_t)row * dv + d] = from_float<T>(o * inv);
   }
