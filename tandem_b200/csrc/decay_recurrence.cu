@@ -9,10 +9,10 @@
 // position * freq[i], in float32), and a constant factor on k after the rotation.
 // `decay_recurrence_scan` walks each request's tokens in order from the state its slot holds and
 // leaves the new state there.  The columns of S are independent, so a block owns 32 of them for one
-// (request, head); warp w of the block holds rows [32 w, 32 w + 32) of those columns in registers.
+// (request, head); warp w of the block holds a few rows (8, or 32 for large keys) of those columns in registers.
 // Tokens are staged sixteen at a time in shared memory (two stages, the next one copied in while
-// this one is worked through); per token a thread does 32 updates of its state and 32 multiply-adds
-// of its part of o, and the parts of the warps are summed in warp order after the sixteen.  The order of operations for a token never depends on how the request was cut
+// this one is worked through); per token a thread updates its rows of the state and multiplies them
+// into its part of o, and the parts of the warps are summed in warp order after the sixteen.  The order of operations for a token never depends on how the request was cut
 // into steps or on the batch, so the state and the output are the same bits under any schedule.
 // `decay_recurrence_post` divides o by a root mean square (per head without weight, or over all
 // heads with a weight), multiplies by a gate (SiLU or sigmoid of its own projection) and rounds to
@@ -93,8 +93,10 @@ __device__ __forceinline__ void dr_load_stage(const float* proj, int stride, int
   asm volatile("cp.async.commit_group;" ::: "memory");
 }
 
-// grid (ceil(dv / 32), H, requests); block = ceil(dk / 32) warps.  Two stages of sixteen tokens: the
-// next one is on its way while this one is worked through.
+// grid (ceil(dv / 32), H, requests); block = ceil(dk / R) warps, each holding R rows of the block's 32 columns
+// (R = 8 gives a scheduler four warps to choose from at a key size of 128; R = 32 serves key sizes beyond 256).
+// Two stages of sixteen tokens: the next one is on its way while this one is worked through.
+template <int R>
 __global__ void decay_recurrence_scan_kernel(const float* __restrict__ proj, int stride, const int* __restrict__ cu_seqlens,
                                              const int* __restrict__ state_slots, float* __restrict__ state,
                                              const float* __restrict__ decay, float* __restrict__ out, int H, int dk, int dv) {
@@ -102,7 +104,7 @@ __global__ void decay_recurrence_scan_kernel(const float* __restrict__ proj, int
   pdl_launch_dependents();
   pdl_wait();
   const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = blockDim.x >> 5;
-  const int dkp = nw * 32;  // dk rounded up to whole warps
+  const int dkp = nw * R;  // dk rounded up to whole warps
   const int stage_floats = 2 * DR_CHUNK * dkp + DR_CHUNK * 32;  // q, k, v of a stage
   float* part_s = smem + 2 * stage_floats;                      // [DR_CHUNK][nw][32]
   const int h = blockIdx.y, b = blockIdx.z;
@@ -112,10 +114,10 @@ __global__ void decay_recurrence_scan_kernel(const float* __restrict__ proj, int
   if (t1 <= t0) return;
   const float g = decay[h];
   float* S = state + (((size_t)state_slots[b] * H + h) * dk) * dv;
-  float s[32];
+  float s[R];
 #pragma unroll
-  for (int i = 0; i < 32; ++i) {
-    const int d = w * 32 + i;
+  for (int i = 0; i < R; ++i) {
+    const int d = w * R + i;
     s[i] = (col_ok && d < dk) ? S[(size_t)d * dv + j] : 0.f;
   }
   for (int e = threadIdx.x; e < 2 * stage_floats; e += blockDim.x) smem[e] = 0.f;  // rows beyond dk and columns beyond dv stay zero
@@ -142,11 +144,11 @@ __global__ void decay_recurrence_scan_kernel(const float* __restrict__ proj, int
     const float* v_s = k_s + DR_CHUNK * dkp;
     for (int c = 0; c < n; ++c) {
       const float vj = v_s[c * 32 + lane];
-      const float4* kc = reinterpret_cast<const float4*>(k_s + c * dkp + w * 32);
-      const float4* qc = reinterpret_cast<const float4*>(q_s + c * dkp + w * 32);
+      const float4* kc = reinterpret_cast<const float4*>(k_s + c * dkp + w * R);
+      const float4* qc = reinterpret_cast<const float4*>(q_s + c * dkp + w * R);
       float part[4] = {0.f, 0.f, 0.f, 0.f};  // four chains: i mod 4; summed in a fixed order
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {
+      for (int i = 0; i < R / 4; ++i) {
         const float4 k4 = kc[i], q4 = qc[i];
         s[4 * i] = fmaf(k4.x, vj, g * s[4 * i]);
         s[4 * i + 1] = fmaf(k4.y, vj, g * s[4 * i + 1]);
@@ -168,8 +170,8 @@ __global__ void decay_recurrence_scan_kernel(const float* __restrict__ proj, int
     // the next turn's loads go into the stage that was read two turns ago, and its parts are written behind its own barrier
   }
 #pragma unroll
-  for (int i = 0; i < 32; ++i) {
-    const int d = w * 32 + i;
+  for (int i = 0; i < R; ++i) {
+    const int d = w * R + i;
     if (col_ok && d < dk) S[(size_t)d * dv + j] = s[i];
   }
 }
@@ -231,14 +233,16 @@ int tb_decay_recurrence_scan(void* stream, const float* proj, int stride, const 
                              float* state, const float* decay, float* out, int requests, int H, int dk, int dv) {
   if (requests <= 0) return 0;
   if (H <= 0 || dk <= 0 || dk > 1024 || dv <= 0 || H > 65535 || requests > 65535) return TB_ERR_BAD_SIZE;
-  const int nw = (dk + 31) / 32;
-  const size_t smem = (size_t)(2 * (2 * tb::DR_CHUNK * nw * 32 + tb::DR_CHUNK * 32) + tb::DR_CHUNK * nw * 32) * sizeof(float);
+  const int R = dk <= 256 ? 8 : 32;
+  const int nw = (dk + R - 1) / R, dkp = nw * R;
+  const size_t smem = (size_t)(2 * (2 * tb::DR_CHUNK * dkp + tb::DR_CHUNK * 32) + tb::DR_CHUNK * nw * 32) * sizeof(float);
+  auto kernel = R == 8 ? tb::decay_recurrence_scan_kernel<8> : tb::decay_recurrence_scan_kernel<32>;
   if (smem > 48 * 1024) {
-    const cudaError_t e = cudaFuncSetAttribute(tb::decay_recurrence_scan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
   }
-  return tb::launch(tb::decay_recurrence_scan_kernel, dim3((dv + 31) / 32, H, requests), dim3(nw * 32), smem, stream, proj, stride,
-                    cu_seqlens, state_slots, state, decay, out, H, dk, dv);
+  return tb::launch(kernel, dim3((dv + 31) / 32, H, requests), dim3(nw * 32), smem, stream, proj, stride, cu_seqlens, state_slots,
+                    state, decay, out, H, dk, dv);
 }
 
 // o float32 [T, H dv]; gate float32 rows of H dv values (stride gate_stride) or null; weight [H dv] or null (mode 1).

@@ -443,17 +443,35 @@ __global__ void scale_softcap_kernel(float* __restrict__ x, long long n, float s
 // ---------------------------------------------------------------------------------------------
 // y[t, c] = act(x[t, c] + bias[c]) for a float32 product x, rounded to T.  act 0: none, 1: the tanh
 // form of GELU, 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))), 2: SiLU.  bias may be null.
+__device__ __forceinline__ float bias_act_one(float z, int act) {
+  if (act == 1) return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+  if (act == 2) return z / (1.f + expf(-z));
+  return z;
+}
+
 template <typename T>
 __global__ void bias_act_kernel(const float* __restrict__ x, const float* __restrict__ bias, T* __restrict__ y, long long total,
                                 int N, int act) {
   pdl_launch_dependents();
   pdl_wait();
-  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
-    float z = x[i] + (bias ? bias[i % N] : 0.f);
-    if (act == 1) z = 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
-    else if (act == 2) z = z / (1.f + expf(-z));
-    y[i] = from_float<T>(z);
+  if ((N & 3) == 0) {  // four elements a turn: 16-byte loads, one 8- or 16-byte store
+    const long long quads = total >> 2;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < quads; i += (long long)gridDim.x * blockDim.x) {
+      float4 z = reinterpret_cast<const float4*>(x)[i];
+      if (bias) {
+        const float4 b = *reinterpret_cast<const float4*>(bias + (i << 2) % N);
+        z.x += b.x; z.y += b.y; z.z += b.z; z.w += b.w;
+      }
+      z.x = bias_act_one(z.x, act); z.y = bias_act_one(z.y, act); z.z = bias_act_one(z.z, act); z.w = bias_act_one(z.w, act);
+      if (sizeof(T) == 2)
+        reinterpret_cast<uint2*>(y)[i] = make_uint2(pack2(z.x, z.y), pack2(z.z, z.w));
+      else
+        reinterpret_cast<float4*>(y)[i] = z;
+    }
+    return;
   }
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x)
+    y[i] = from_float<T>(bias_act_one(x[i] + (bias ? bias[i % N] : 0.f), act));
 }
 
 // residual[t, c] += (a[t, c] + a_bias[c]) + (b[t, c] + b_bias[c]): the outputs of two sublayers that
@@ -462,6 +480,23 @@ __global__ void add_pair_kernel(float* __restrict__ residual, const float* __res
                                 const float* __restrict__ b, const float* __restrict__ b_bias, long long total, int N) {
   pdl_launch_dependents();
   pdl_wait();
+  if ((N & 3) == 0) {
+    const long long quads = total >> 2;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < quads; i += (long long)gridDim.x * blockDim.x) {
+      const int c = (int)((i << 2) % N);
+      float4 s = reinterpret_cast<const float4*>(a)[i];
+      if (a_bias) { const float4 t = *reinterpret_cast<const float4*>(a_bias + c); s.x += t.x; s.y += t.y; s.z += t.z; s.w += t.w; }
+      if (b) {
+        float4 u = reinterpret_cast<const float4*>(b)[i];
+        if (b_bias) { const float4 t = *reinterpret_cast<const float4*>(b_bias + c); u.x += t.x; u.y += t.y; u.z += t.z; u.w += t.w; }
+        s.x += u.x; s.y += u.y; s.z += u.z; s.w += u.w;
+      }
+      float4 r = reinterpret_cast<float4*>(residual)[i];
+      r.x += s.x; r.y += s.y; r.z += s.z; r.w += s.w;
+      reinterpret_cast<float4*>(residual)[i] = r;
+    }
+    return;
+  }
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
     const int c = (int)(i % N);
     float s = a[i] + (a_bias ? a_bias[c] : 0.f);
@@ -541,7 +576,7 @@ int tb_bias_act(void* stream, const float* x, const float* bias, void* y, int ro
   const long long total = (long long)rows * N;
   if (total <= 0) return 0;
   if (act < 0 || act > 2) return TB_ERR_BAD_SIZE;
-  long long blocks = (total + 255) / 256;
+  long long blocks = (total / 4 + 255) / 256 + 1;
   if (blocks > 148 * 16) blocks = 148 * 16;
   TB_DISPATCH_DTYPE(dtype, tb::launch(tb::bias_act_kernel<T>, dim3((int)blocks), dim3(256), 0, stream, x, bias, (T*)y, total, N, act));
 }
