@@ -9,7 +9,7 @@
 // position * freq[i], in float32), and a constant factor on k after the rotation.
 // `decay_recurrence_scan` walks each request's tokens in order from the state its slot holds and
 // leaves the new state there.  The columns of S are independent, so a block owns 32 of them for one
-// (request, head); warp w of the block holds a few rows (8, or 32 for large keys) of those columns in registers.
+// (request, head); warp w of the block holds a few rows (16, or 32 for large keys) of those columns in registers.
 // Tokens are staged sixteen at a time in shared memory (two stages, the next one copied in while
 // this one is worked through); per token a thread updates its rows of the state and multiplies them
 // into its part of o, and the parts of the warps are summed in warp order after the sixteen.  The order of operations for a token never depends on how the request was cut
@@ -94,7 +94,8 @@ __device__ __forceinline__ void dr_load_stage(const float* proj, int stride, int
 }
 
 // grid (ceil(dv / 32), H, requests); block = ceil(dk / R) warps, each holding R rows of the block's 32 columns
-// (R = 8 gives a scheduler four warps to choose from at a key size of 128; R = 32 serves key sizes beyond 256).
+// (R = 16 gives a scheduler two warps to choose from at a key size of 128 and costs 0.6 of the instructions of
+// R = 8, which was bound by instruction issue: 60 a token and warp; R = 32 serves key sizes beyond 512).
 // Two stages of sixteen tokens: the next one is on its way while this one is worked through.
 template <int R>
 __global__ void decay_recurrence_scan_kernel(const float* __restrict__ proj, int stride, const int* __restrict__ cu_seqlens,
@@ -233,10 +234,10 @@ int tb_decay_recurrence_scan(void* stream, const float* proj, int stride, const 
                              float* state, const float* decay, float* out, int requests, int H, int dk, int dv) {
   if (requests <= 0) return 0;
   if (H <= 0 || dk <= 0 || dk > 1024 || dv <= 0 || H > 65535 || requests > 65535) return TB_ERR_BAD_SIZE;
-  const int R = dk <= 256 ? 8 : 32;
+  const int R = dk <= 512 ? 16 : 32;
   const int nw = (dk + R - 1) / R, dkp = nw * R;
   const size_t smem = (size_t)(2 * (2 * tb::DR_CHUNK * dkp + tb::DR_CHUNK * 32) + tb::DR_CHUNK * nw * 32) * sizeof(float);
-  auto kernel = R == 8 ? tb::decay_recurrence_scan_kernel<8> : tb::decay_recurrence_scan_kernel<32>;
+  auto kernel = R == 16 ? tb::decay_recurrence_scan_kernel<16> : tb::decay_recurrence_scan_kernel<32>;
   if (smem > 48 * 1024) {
     const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;

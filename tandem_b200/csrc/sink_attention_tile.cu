@@ -4,7 +4,7 @@
 // The host cuts every request's new tokens into query tiles; one block of four warps runs one tile
 // for one kv head.  A tile's 64 rows are (token, query head of the group) pairs, token-major, so one
 // pass over the keys serves all the query heads that share the kv head.  Keys and values come from
-// the request's pages in stages of 64 keys, 16 bytes per cp.async, two stages in flight; a stage's
+// the request's pages in stages of 64 keys, 16 bytes per cp.async (a thread per row), two stages in flight; a stage's
 // rows keep a padded row-major layout whatever the cache's own tile layout is.  Per stage a warp
 // computes S = Q K^T for its 16 rows with mma.sync, then in float32: scale, cap * tanh(s / cap), the
 // bias by distance, the mask (causal, window, kept first tokens), the online softmax, whose starting
@@ -24,6 +24,7 @@ namespace tb {
 constexpr int DK = TB_DK, DV = TB_DV;
 static_assert(DK % 16 == 0 && DV % 16 == 0 && DK >= 16 && DV >= 16 && DK <= 128 && DV <= 128, "sizes: multiples of 16 up to 128");
 constexpr int ST_WARPS = 4, ST_THREADS = ST_WARPS * 32, ST_BM = ST_WARPS * 16, ST_KEYS = 64;
+static_assert(ST_THREADS == 2 * ST_KEYS, "one thread per key row and one per value row of a stage");
 constexpr int QP = DK + 8, KP = DK + 8, VP = DV + 8;  // padded rows: ldmatrix without bank conflicts
 constexpr int ST_TILE_INTS = 4;                        // first token row, request, first position, number of tokens
 constexpr float LOG2E = 1.4426950408889634f;
@@ -50,28 +51,38 @@ __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commi
 template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
 // Keys [base, base + 64) restricted to [lo, hi) into one stage; rows outside are zeroed (values must
-// not be NaN: their weights are zero).
+// not be NaN: their weights are zero).  Threads 0..63 bring one key row each, threads 64..127 one value
+// row each: one look at the block table and one tile address per row, then its 16-byte pieces.
+template <int D, int PITCH>
+__device__ __forceinline__ void load_row(const __nv_bfloat16* cache, const int* table, int kvh, int nkv, int ps, int key, bool in_range,
+                                         __nv_bfloat16* dst_row) {
+  const int page = in_range ? table[key / ps] : -1;
+  if (page < 0) {
+#pragma unroll
+    for (int c = 0; c < D / 8; ++c) *reinterpret_cast<uint4*>(dst_row + c * 8) = make_uint4(0, 0, 0, 0);
+    return;
+  }
+  const int r = key % ps;
+  const __nv_bfloat16* tile = cache + cache_tile(page, kvh, nkv, ps, D);
+  if (cache_swizzled<__nv_bfloat16>(D, ps)) {  // [row group][column block][rows of the group][64], chunks XOR-ed with the row
+    const int rows = ps < 8 ? ps : 8, group = ps < 8 ? 0 : r >> 3, rr = ps < 8 ? r : r & 7;
+#pragma unroll
+    for (int c = 0; c < D / 8; ++c)
+      cp_async16(dst_row + c * 8, tile + ((group * (D >> 6) + (c >> 3)) * rows + rr) * 64 + (((c & 7) ^ (r & 7)) << 3));
+  } else {
+#pragma unroll
+    for (int c = 0; c < D / 8; ++c) cp_async16(dst_row + c * 8, tile + r * D + c * 8);
+  }
+}
+
 __device__ __forceinline__ void load_stage(const TileArgs& a, const int* table, int kvh, int base, int lo, int hi,
                                            __nv_bfloat16* ks, __nv_bfloat16* vs, int tid) {
-  const int ps = a.page_size;
-  for (int i = tid; i < ST_KEYS * (DK / 8); i += ST_THREADS) {
-    const int row = i / (DK / 8), c = i % (DK / 8), key = base + row;
-    __nv_bfloat16* dst = ks + row * KP + c * 8;
-    const int page = (key >= lo && key < hi) ? table[key / ps] : -1;
-    if (page >= 0)
-      cp_async16(dst, a.k_cache + cache_tile(page, kvh, a.nkv, ps, DK) + cache_offset<__nv_bfloat16>(key % ps, c * 8, ps, DK));
-    else
-      *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
-  }
-  for (int i = tid; i < ST_KEYS * (DV / 8); i += ST_THREADS) {
-    const int row = i / (DV / 8), c = i % (DV / 8), key = base + row;
-    __nv_bfloat16* dst = vs + row * VP + c * 8;
-    const int page = (key >= lo && key < hi) ? table[key / ps] : -1;
-    if (page >= 0)
-      cp_async16(dst, a.v_cache + cache_tile(page, kvh, a.nkv, ps, DV) + cache_offset<__nv_bfloat16>(key % ps, c * 8, ps, DV));
-    else
-      *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
-  }
+  const int row = tid & (ST_KEYS - 1), key = base + row;
+  const bool in_range = key >= lo && key < hi;
+  if (tid < ST_KEYS)
+    load_row<DK, KP>(a.k_cache, table, kvh, a.nkv, a.page_size, key, in_range, ks + row * KP);
+  else
+    load_row<DV, VP>(a.v_cache, table, kvh, a.nkv, a.page_size, key, in_range, vs + row * VP);
 }
 
 __global__ void __launch_bounds__(ST_THREADS) sink_attention_tile_kernel(const TileArgs a) {
@@ -169,6 +180,9 @@ __global__ void __launch_bounds__(ST_THREADS) sink_attention_tile_kernel(const T
           mma_bf16_16816(s[2 * sub + 1], qf[ks], b[2], b[3]);
         }
       }
+      // every key of the stage visible to every row of the warp: no mask to work out
+      const bool whole = base >= lo && base + ST_KEYS <= hi && base + ST_KEYS - 1 <= warp_first_pos &&
+                         (W <= 0 || base > warp_last_pos - W || base + ST_KEYS <= a.keep_first);
       float tile_max[2] = {-INFINITY, -INFINITY};
 #pragma unroll
       for (int nt = 0; nt < 8; ++nt)
@@ -177,7 +191,7 @@ __global__ void __launch_bounds__(ST_THREADS) sink_attention_tile_kernel(const T
           const int r = e >> 1, key = base + nt * 8 + (lane & 3) * 2 + (e & 1), q = qpos[r];
           float v = s[nt][e] * a.scale;
           if (a.cap > 0.f) v = a.cap * (1.f - __fdividef(2.f, __expf(2.f * v * inv_cap) + 1.f));  // cap * tanh(v / cap)
-          const bool seen = key >= lo && key < hi && key <= q && (W <= 0 || key > q - W || key < a.keep_first);
+          const bool seen = whole || (key >= lo && key < hi && key <= q && (W <= 0 || key > q - W || key < a.keep_first));
           if (seen && a.bias) v += __ldg(a.bias + (size_t)min(q - key, a.max_dist) * a.nh + head[r]);
           v = seen ? v * LOG2E : -INFINITY;
           s[nt][e] = v;
