@@ -98,9 +98,9 @@ __device__ __forceinline__ void dr_load_stage(const float* proj, int stride, int
 // R = 8, which was bound by instruction issue: 60 a token and warp; R = 32 serves key sizes beyond 512).
 // Two stages of sixteen tokens: the next one is on its way while this one is worked through.
 template <int R>
-__global__ void decay_recurrence_scan_kernel(const float* __restrict__ proj, int stride, const int* __restrict__ cu_seqlens,
-                                             const int* __restrict__ state_slots, float* __restrict__ state,
-                                             const float* __restrict__ decay, float* __restrict__ out, int H, int dk, int dv) {
+__device__ __forceinline__ void decay_recurrence_scan_body(const float* __restrict__ proj, int stride, const int* __restrict__ cu_seqlens,
+                                                           const int* __restrict__ state_slots, float* __restrict__ state,
+                                                           const float* __restrict__ decay, float* __restrict__ out, int H, int dk, int dv) {
   extern __shared__ __align__(16) float smem[];
   pdl_launch_dependents();
   pdl_wait();
@@ -177,6 +177,21 @@ __global__ void decay_recurrence_scan_kernel(const float* __restrict__ proj, int
   }
 }
 
+// Key sizes up to 256 run blocks of up to 512 threads with the registers the compiler wants; larger ones run blocks
+// of up to 1,024 threads, which leaves 64 registers a thread.
+__global__ void decay_recurrence_scan_kernel(const float* __restrict__ proj, int stride, const int* __restrict__ cu_seqlens,
+                                             const int* __restrict__ state_slots, float* __restrict__ state,
+                                             const float* __restrict__ decay, float* __restrict__ out, int H, int dk, int dv) {
+  decay_recurrence_scan_body<16>(proj, stride, cu_seqlens, state_slots, state, decay, out, H, dk, dv);
+}
+template <int R>
+__global__ void __launch_bounds__(1024)
+decay_recurrence_scan_wide_kernel(const float* __restrict__ proj, int stride, const int* __restrict__ cu_seqlens,
+                                  const int* __restrict__ state_slots, float* __restrict__ state, const float* __restrict__ decay,
+                                  float* __restrict__ out, int H, int dk, int dv) {
+  decay_recurrence_scan_body<R>(proj, stride, cu_seqlens, state_slots, state, decay, out, H, dk, dv);
+}
+
 // One block per token.  mode 0: each head divided by its own root mean square; mode 1: all heads
 // together, times `weight` [H dv].  Then times gate_act(gate), rounded to T.
 template <typename T>
@@ -237,7 +252,8 @@ int tb_decay_recurrence_scan(void* stream, const float* proj, int stride, const 
   const int R = dk <= 512 ? 16 : 32;
   const int nw = (dk + R - 1) / R, dkp = nw * R;
   const size_t smem = (size_t)(2 * (2 * tb::DR_CHUNK * dkp + tb::DR_CHUNK * 32) + tb::DR_CHUNK * nw * 32) * sizeof(float);
-  auto kernel = R == 16 ? tb::decay_recurrence_scan_kernel<16> : tb::decay_recurrence_scan_kernel<32>;
+  auto kernel = dk <= 256 ? tb::decay_recurrence_scan_kernel
+                          : (R == 16 ? tb::decay_recurrence_scan_wide_kernel<16> : tb::decay_recurrence_scan_wide_kernel<32>);
   if (smem > 48 * 1024) {
     const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;

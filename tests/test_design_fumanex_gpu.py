@@ -383,7 +383,7 @@ def test_cap_bias_and_sink_in_the_kernel():
         assert (got - ref16).abs().max() < 3e-2, (page_size, cuts[:2])
 
 
-@pytest.mark.parametrize("dk,dv,H", [(32, 64, 4), (20, 8, 3), (96, 33, 1), (128, 128, 2)])
+@pytest.mark.parametrize("dk,dv,H", [(32, 64, 4), (20, 8, 3), (96, 33, 1), (128, 128, 2), (544, 16, 1), (6, 70, 2)])
 def test_the_recurrence_kernel_alone(dk, dv, H):
     """Two requests of unequal length in one launch, then their continuation from the stored state; a third
     request takes over a row of the state tensor that was in use."""
