@@ -5,7 +5,10 @@ the mixer does not know which model it serves.
 
 One fused projection (rows [q | k | v]) with a float32 result; one kernel adds the biases,
 normalises q and k, mixes and stores k and v; one kernel attends over the paged cache (the tokens
-of the step included, so a portion sees itself through the cache).  The output projection comes
+of the step included, so a portion sees itself through the cache): one warp per token and head
+in float32 and wherever the others do not take the shape, query tiles on the tensor cores for
+bfloat16 steps that bring prompt portions, a token's keys cut over several blocks for bfloat16
+steps of single tokens.  The output projection comes
 back with its bias not yet added (``deferred.Unsummed``) when the arrangement asks for that.
 """
 
