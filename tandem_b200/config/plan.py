@@ -42,7 +42,7 @@ class ParamSpec:
 @dataclass(frozen=True)
 class PartSpec:
     """Base of every spec: ``kind`` picks the implementation in the registry, within the spec's
-    ``family`` ("mixer", "feed_forward", "norm", "position")."""
+    ``family`` ("mixer", "feed_forward", "norm", "position", "connection")."""
 
     kind: str
     family = None  # set by the base class of each family
@@ -163,6 +163,54 @@ class DecayRecurrenceSpec(MixerSpec):
 
 
 @dataclass(frozen=True)
+class SelectiveRecurrenceSpec(MixerSpec):
+    """A state-space recurrence whose decay and step size are made from the token (the "state-space
+    duality" form): one projection laid out [z: H P | x: H P | B: G N | C: G N | dt: H] (H heads of P
+    values, G groups of N state rows; head h reads group h // (H / G)); x, B and C pass a causal
+    convolution of ``conv_taps`` taps per channel (with bias) and SiLU; dt <- softplus(dt + dt_bias);
+    S <- exp(-exp(A_log_h) dt) S + dt B x^T, y = S^T C + D_h x per head, S [N, P] in float32; y times
+    SiLU(z), divided by its root mean square in ``norm_groups`` equal parts, times a weight, then the
+    output projection.  The state of a request is S of every head and the last ``conv_taps - 1`` inputs
+    of the convolution.  Checkpoint tensors ``<prefix>.in``, ``.conv`` [channels, taps], ``.conv.b``,
+    ``.dt_bias``, ``.A_log``, ``.D``, ``.norm``, ``.o``; ``names`` renames them (local -> suffix)."""
+
+    hidden_size: int = 0
+    num_heads: int = 0
+    value_dim: int = 0  # P
+    state_dim: int = 0  # N
+    groups: int = 1  # G
+    conv_taps: int = 1
+    norm_groups: int = 1
+    norm_eps: float = 1e-6
+    names: tuple = ()
+
+
+@dataclass(frozen=True)
+class LatentAttentionSpec(MixerSpec):
+    """Causal softmax attention whose keys and values are expanded from a latent of ``latent_dim``
+    numbers per token (RMS-normed with a weight), plus one rotated key part of ``rotary_dim``
+    numbers that all heads share; a query head is [``head_dim`` unrotated | ``rotary_dim`` rotated].
+    The rotation (rotate_half pairing, angle = position * base^(-2 i / rotated_dims)) turns the first
+    ``rotated_dims`` numbers of the rotated part.
+    Only the latent and the rotated key part are cached.  ``gate``: "sigmoid" multiplies the
+    concatenated heads by sigmoid of a projection of the mixer's input, "none" leaves them.
+    Checkpoint tensors ``<prefix>.q``, ``.dkv``, ``.dkv.norm``, ``.uk``, ``.uv``, ``.g``, ``.o``."""
+
+    hidden_size: int = 0
+    num_heads: int = 0
+    head_dim: int = 0  # unrotated query/key dimensions per head
+    rotary_dim: int = 0
+    rotated_dims: int = 0
+    rotary_base: float = 10000.0
+    value_dim: int = 0
+    latent_dim: int = 0
+    scale: float = 1.0
+    norm_eps: float = 1e-6
+    gate: str = "sigmoid"
+    names: tuple = ()
+
+
+@dataclass(frozen=True)
 class FeedForwardSpec(PartSpec):
     family = "feed_forward"
     prefix: str = ""
@@ -172,6 +220,26 @@ class FeedForwardSpec(PartSpec):
 class GatedMLPSpec(FeedForwardSpec):
     hidden_size: int = 0
     intermediate_size: int = 0
+    activation: str = "silu"
+    names: tuple = ()  # (local, checkpoint suffix) for "gate", "up", "down" where they are not <x>_proj.weight
+    float32_output: bool = False  # the down projection comes back unrounded
+
+
+@dataclass(frozen=True)
+class RoutedMLPSpec(FeedForwardSpec):
+    """``num_experts`` gated feed-forwards (down(act(gate x) * up x), no biases) of which a token uses
+    ``top_k``: router logits W_router x in float32, scores by ``score`` ("sigmoid" | "softmax"), the
+    ``top_k`` largest scores chosen, their scores divided by their sum (+ 1e-20) where ``normalize``,
+    times ``route_scale``; the output is the weighted sum of the chosen experts' outputs.  Checkpoint
+    tensors ``<prefix>.router`` [experts, hidden], ``<prefix>.e<i>.gate``, ``.up``, ``.down``."""
+
+    hidden_size: int = 0
+    intermediate_size: int = 0  # of one expert
+    num_experts: int = 0
+    top_k: int = 1
+    score: str = "sigmoid"
+    normalize: bool = True
+    route_scale: float = 1.0
     activation: str = "silu"
 
 
@@ -185,6 +253,24 @@ class DenseMLPSpec(FeedForwardSpec):
     activation: str = "gelu_tanh"
     bias: bool = True
     names: tuple = ()
+
+
+@dataclass(frozen=True)
+class ConnectionSpec(PartSpec):
+    family = "connection"
+
+
+@dataclass(frozen=True)
+class StreamLinkSpec(ConnectionSpec):
+    """How one sublayer hangs on a residual of ``streams`` parallel streams X_1 .. X_s: it reads
+    u = sum_s in[s] X_s and, with its output y, every stream becomes (all from the old ones)
+    X_t <- sum_s mix[s, t] X_s + mult * out[t] * y.  ``prefix`` names the checkpoint tensors
+    ``<prefix>.in`` [s], ``.out`` [s], ``.mix`` [s, s] (indexed [from, to]); None: one stream with
+    in = out = mix = 1, which is the plain residual sum x <- x + mult * y."""
+
+    streams: int = 1
+    mult: float = 1.0
+    prefix: Optional[str] = None
 
 
 @dataclass(frozen=True)
@@ -234,13 +320,15 @@ class RunStep:
 @dataclass(frozen=True)
 class EmbeddingSpec:
     """Start of the residual stream: ``scale * table[token]``, plus ``positions[position]`` where
-    the model has a learned table of absolute positions (a checkpoint tensor [max_position, hidden])."""
+    the model has a learned table of absolute positions (a checkpoint tensor [max_position, hidden]);
+    written ``copies`` times side by side for arrangements that keep several streams."""
 
     vocab_size: int
     hidden_size: int
     weight: str
     scale: float = 1.0
     positions: Optional[str] = None
+    copies: int = 1  # the residual starts as so many equal streams side by side, [T, copies * hidden]
 
 
 @dataclass(frozen=True)

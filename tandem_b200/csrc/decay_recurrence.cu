@@ -17,6 +17,17 @@
 // `decay_recurrence_post` divides o by a root mean square (per head without weight, or over all
 // heads with a weight), multiplies by a gate (SiLU or sigmoid of its own projection) and rounds to
 // the storage type of the output projection's input.
+//
+// The scan also serves recurrences whose decay is made from the token (`decay_tok` [T, H]: the decay of
+// head h at token t replaces the fixed one) and whose q and k are shared by groups of heads (`qk_heads`
+// sets of q and k for H heads of v: head h reads set h / (H / qk_heads)); where q, k and v start in a row
+// and how far apart the states of two slots lie are arguments.  For such a "selective" state-space layer
+// S <- exp(-exp(A_log_h) dt) S + dt B x^T, y = S^T C + D_h x  is the scan with q = C, k = B, v = dt x and
+// decay exp(-exp(A_log_h) dt): `selective_prep` makes those rows from the layer's projection (a causal
+// convolution per channel over the request's earlier inputs, the last of which it finds in the request's
+// state, SiLU, softplus of the step size), `conv_state_update` leaves the newest inputs in the state, and
+// `selective_post` adds D x, multiplies by SiLU(z), then divides by the root mean square in equal parts
+// of the row and multiplies by a weight.
 #include "common.cuh"
 
 namespace tb {
@@ -65,7 +76,9 @@ __device__ __forceinline__ void dr_cp_async16(void* dst, const void* src) {
 // Tokens [c0, c0 + n) of one head into a stage: q and k rows of dk floats (row pitch dkp), 32 value columns.
 // `vec`: every row piece starts on 16 bytes, so the copies are asynchronous 16-byte ones.
 __device__ __forceinline__ void dr_load_stage(const float* proj, int stride, int c0, int n, int q_col, int k_col, int v_col,
-                                              int v_cols, int dk, int dkp, float* q_s, float* k_s, float* v_s, bool vec) {
+                                              int v_cols, int dk, int dkp, float* q_s, float* k_s, float* v_s, bool vec,
+                                              const float* decay_tok, int H, int h, float* g_s) {
+  if (decay_tok && (int)threadIdx.x < n) g_s[threadIdx.x] = decay_tok[(size_t)(c0 + threadIdx.x) * H + h];  // read two turns later
   if (vec) {
     const int per_row = dk >> 2;
     for (int e = threadIdx.x; e < n * per_row; e += blockDim.x) {
@@ -100,21 +113,23 @@ __device__ __forceinline__ void dr_load_stage(const float* proj, int stride, int
 template <int R>
 __device__ __forceinline__ void decay_recurrence_scan_body(const float* __restrict__ proj, int stride, const int* __restrict__ cu_seqlens,
                                                            const int* __restrict__ state_slots, float* __restrict__ state,
-                                                           const float* __restrict__ decay, float* __restrict__ out, int H, int dk, int dv) {
+                                                           const float* __restrict__ decay, float* __restrict__ out, int H, int dk, int dv,
+                                                           const float* __restrict__ decay_tok, int qk_heads, int q_off, int k_off,
+                                                           int v_off, long long state_stride) {
   extern __shared__ __align__(16) float smem[];
   pdl_launch_dependents();
   pdl_wait();
   const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = blockDim.x >> 5;
   const int dkp = nw * R;  // dk rounded up to whole warps
-  const int stage_floats = 2 * DR_CHUNK * dkp + DR_CHUNK * 32;  // q, k, v of a stage
+  const int stage_floats = 2 * DR_CHUNK * dkp + DR_CHUNK * 32 + DR_CHUNK;  // q, k, v and the decays of a stage
   float* part_s = smem + 2 * stage_floats;                      // [DR_CHUNK][nw][32]
   const int h = blockIdx.y, b = blockIdx.z;
   const int j = blockIdx.x * 32 + lane;       // this thread's column of S
   const bool col_ok = j < dv;
   const int t0 = cu_seqlens[b], t1 = cu_seqlens[b + 1];
   if (t1 <= t0) return;
-  const float g = decay[h];
-  float* S = state + (((size_t)state_slots[b] * H + h) * dk) * dv;
+  const float g_fixed = decay ? decay[h] : 1.f;
+  float* S = state + (size_t)state_slots[b] * state_stride + ((size_t)h * dk) * dv;
   float s[R];
 #pragma unroll
   for (int i = 0; i < R; ++i) {
@@ -123,18 +138,19 @@ __device__ __forceinline__ void decay_recurrence_scan_body(const float* __restri
   }
   for (int e = threadIdx.x; e < 2 * stage_floats; e += blockDim.x) smem[e] = 0.f;  // rows beyond dk and columns beyond dv stay zero
   __syncthreads();
-  const int q_col = h * dk, k_col = H * dk + h * dk, v_col = 2 * H * dk + h * dv + blockIdx.x * 32;
+  const int set = h / (H / qk_heads);  // which q and k the head reads
+  const int q_col = q_off + set * dk, k_col = k_off + set * dk, v_col = v_off + h * dv + blockIdx.x * 32;
   const int v_cols = min(32, dv - blockIdx.x * 32);
-  const bool vec = ((dk | dv | stride) & 3) == 0 && (reinterpret_cast<uintptr_t>(proj) & 15) == 0;
+  const bool vec = ((dk | dv | stride | q_off | k_off | v_off) & 3) == 0 && (reinterpret_cast<uintptr_t>(proj) & 15) == 0;
   dr_load_stage(proj, stride, t0, min(DR_CHUNK, t1 - t0), q_col, k_col, v_col, v_cols, dk, dkp, smem, smem + DR_CHUNK * dkp,
-                smem + 2 * DR_CHUNK * dkp, vec);
+                smem + 2 * DR_CHUNK * dkp, vec, decay_tok, H, h, smem + 2 * DR_CHUNK * dkp + DR_CHUNK * 32);
   int slot = 0;
   for (int c0 = t0; c0 < t1; c0 += DR_CHUNK, slot ^= 1) {
     const int n = min(DR_CHUNK, t1 - c0);
     if (c0 + DR_CHUNK < t1) {
       float* nxt = smem + (slot ^ 1) * stage_floats;
       dr_load_stage(proj, stride, c0 + DR_CHUNK, min(DR_CHUNK, t1 - c0 - DR_CHUNK), q_col, k_col, v_col, v_cols, dk, dkp, nxt,
-                    nxt + DR_CHUNK * dkp, nxt + 2 * DR_CHUNK * dkp, vec);
+                    nxt + DR_CHUNK * dkp, nxt + 2 * DR_CHUNK * dkp, vec, decay_tok, H, h, nxt + 2 * DR_CHUNK * dkp + DR_CHUNK * 32);
       asm volatile("cp.async.wait_group 1;" ::: "memory");
     } else {
       asm volatile("cp.async.wait_group 0;" ::: "memory");
@@ -143,7 +159,9 @@ __device__ __forceinline__ void decay_recurrence_scan_body(const float* __restri
     const float* q_s = smem + slot * stage_floats;
     const float* k_s = q_s + DR_CHUNK * dkp;
     const float* v_s = k_s + DR_CHUNK * dkp;
+    const float* g_s = v_s + DR_CHUNK * 32;
     for (int c = 0; c < n; ++c) {
+      const float g = decay_tok ? g_s[c] : g_fixed;
       const float vj = v_s[c * 32 + lane];
       const float4* kc = reinterpret_cast<const float4*>(k_s + c * dkp + w * R);
       const float4* qc = reinterpret_cast<const float4*>(q_s + c * dkp + w * R);
@@ -181,15 +199,20 @@ __device__ __forceinline__ void decay_recurrence_scan_body(const float* __restri
 // of up to 1,024 threads, which leaves 64 registers a thread.
 __global__ void decay_recurrence_scan_kernel(const float* __restrict__ proj, int stride, const int* __restrict__ cu_seqlens,
                                              const int* __restrict__ state_slots, float* __restrict__ state,
-                                             const float* __restrict__ decay, float* __restrict__ out, int H, int dk, int dv) {
-  decay_recurrence_scan_body<16>(proj, stride, cu_seqlens, state_slots, state, decay, out, H, dk, dv);
+                                             const float* __restrict__ decay, float* __restrict__ out, int H, int dk, int dv,
+                                             const float* __restrict__ decay_tok, int qk_heads, int q_off, int k_off, int v_off,
+                                             long long state_stride) {
+  decay_recurrence_scan_body<16>(proj, stride, cu_seqlens, state_slots, state, decay, out, H, dk, dv, decay_tok, qk_heads, q_off,
+                                 k_off, v_off, state_stride);
 }
 template <int R>
 __global__ void __launch_bounds__(1024)
 decay_recurrence_scan_wide_kernel(const float* __restrict__ proj, int stride, const int* __restrict__ cu_seqlens,
                                   const int* __restrict__ state_slots, float* __restrict__ state, const float* __restrict__ decay,
-                                  float* __restrict__ out, int H, int dk, int dv) {
-  decay_recurrence_scan_body<R>(proj, stride, cu_seqlens, state_slots, state, decay, out, H, dk, dv);
+                                  float* __restrict__ out, int H, int dk, int dv, const float* __restrict__ decay_tok, int qk_heads,
+                                  int q_off, int k_off, int v_off, long long state_stride) {
+  decay_recurrence_scan_body<R>(proj, stride, cu_seqlens, state_slots, state, decay, out, H, dk, dv, decay_tok, qk_heads, q_off,
+                                k_off, v_off, state_stride);
 }
 
 // One block per token.  mode 0: each head divided by its own root mean square; mode 1: all heads
@@ -227,6 +250,93 @@ __global__ void decay_recurrence_post_kernel(const float* __restrict__ o, const 
     yrow[c] = from_float<T>(orow[c] * inv * (weight ? weight[c] : 1.f) * (grow ? act_apply(grow[c], gate_act) : 1.f));
 }
 
+// ---------------------------------------------------------------------------------------------
+// The selective layer's prologue.  proj float32 [T, stride] = [z: inner | u: C channels | dt: H | ...] with the
+// channels u = [x: inner | B: G N | C: G N] and inner = H P.  One thread per (token, channel):
+//   c_t = SiLU(bias + sum_j taps[K-1-j] u_(t-j)),  u before this step's first token from the request's state
+//   (the inputs at positions start-(K-1) .. start-1, zeros in front of the sequence), float32 [slots][K-1][C].
+// Written to rows [x | B | C | dt x] (stride 2 inner + 2 G N) for the scan and the epilogue; the first thread
+// of a head also writes the head's decay exp(-exp(A_log) dt) with dt = softplus(dt + dt_bias).
+__device__ __forceinline__ float softplus_f(float x) { return fmaxf(x, 0.f) + log1pf(expf(-fabsf(x))); }
+
+__global__ void selective_prep_kernel(const float* __restrict__ proj, int stride, const float* __restrict__ taps,
+                                      const float* __restrict__ conv_bias, const float* __restrict__ dt_bias,
+                                      const float* __restrict__ a_log, const float* __restrict__ conv_state, long long state_stride,
+                                      const int* __restrict__ seq_of_token, const int* __restrict__ positions,
+                                      const int* __restrict__ seq_starts, const int* __restrict__ state_slots,
+                                      float* __restrict__ rows, float* __restrict__ decay, long long total, int H, int P, int GN2,
+                                      int K) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int inner = H * P, C = inner + GN2, out_stride = 2 * inner + GN2;
+  for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (long long)gridDim.x * blockDim.x) {
+    const int t = (int)(idx / C), c = (int)(idx % C);
+    const int b = seq_of_token[t];
+    const int local = positions[t] - seq_starts[b];  // tokens of the request in this step in front of this one
+    const float* old = conv_state + (size_t)state_slots[b] * state_stride;
+    float acc = conv_bias[c];
+    for (int j = K - 1; j >= 0; --j) {  // oldest input first
+      const float u = j <= local ? proj[(size_t)(t - j) * stride + inner + c] : old[(size_t)(local - j + K - 1) * C + c];
+      acc = fmaf(taps[(size_t)c * K + (K - 1 - j)], u, acc);
+    }
+    const float v = acc / (1.f + expf(-acc));
+    float* row = rows + (size_t)t * out_stride;
+    row[c] = v;
+    if (c < inner) {
+      const int h = c / P;
+      const float dt = softplus_f(proj[(size_t)t * stride + inner + C + h] + dt_bias[h]);
+      row[inner + GN2 + c] = dt * v;
+      if (c == h * P) decay[(size_t)t * H + h] = expf(-expf(a_log[h]) * dt);
+    }
+  }
+}
+
+// One thread per (request, channel): the last K-1 inputs of the convolution after this step, oldest first.
+__global__ void conv_state_update_kernel(const float* __restrict__ proj, int stride, int col0, float* __restrict__ conv_state,
+                                         long long state_stride, const int* __restrict__ cu_seqlens,
+                                         const int* __restrict__ state_slots, int requests, int C, int K) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= (long long)requests * C) return;
+  const int b = (int)(idx / C), c = (int)(idx % C);
+  const int t0 = cu_seqlens[b], n = cu_seqlens[b + 1] - t0;
+  if (n <= 0) return;
+  float* st = conv_state + (size_t)state_slots[b] * state_stride;
+  for (int k = 0; k < K - 1; ++k) {  // entry k moves down by n places: st[k + n] is read before any turn writes it
+    const int i = n - (K - 1) + k;   // the token of this step that the entry holds, if not negative
+    st[(size_t)k * C + c] = i >= 0 ? proj[(size_t)(t0 + i) * stride + col0 + c] : st[(size_t)(k + n) * C + c];
+  }
+}
+
+// y = (o + D_h x) * SiLU(z), divided by its root mean square in `parts` equal parts of the row, times weight.
+// grid (tokens, parts).  o float32 [T, H P]; x at rows[t][0 .. H P); z at proj[t][0 .. H P).
+template <typename T>
+__global__ void selective_post_kernel(const float* __restrict__ o, const float* __restrict__ rows, int rows_stride,
+                                      const float* __restrict__ z, int z_stride, const float* __restrict__ D,
+                                      const float* __restrict__ weight, T* __restrict__ y, int H, int P, int parts, float eps) {
+  __shared__ float scratch[33];
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x, part = blockIdx.y, n = H * P / parts, c0 = part * n;
+  const float* orow = o + (size_t)t * H * P;
+  const float* xrow = rows + (size_t)t * rows_stride;
+  const float* zrow = z + (size_t)t * z_stride;
+  float ss = 0.f;
+  for (int c = c0 + threadIdx.x; c < c0 + n; c += blockDim.x) {
+    const float zz = zrow[c];
+    const float v = fmaf(D[c / P], xrow[c], orow[c]) * (zz / (1.f + expf(-zz)));
+    ss = fmaf(v, v, ss);
+  }
+  ss = block_sum(ss, scratch);
+  const float inv = rsqrtf(ss / (float)n + eps);
+  for (int c = c0 + threadIdx.x; c < c0 + n; c += blockDim.x) {
+    const float zz = zrow[c];
+    const float v = fmaf(D[c / P], xrow[c], orow[c]) * (zz / (1.f + expf(-zz)));
+    y[(size_t)t * H * P + c] = from_float<T>(v * inv * weight[c]);
+  }
+}
+
 }  // namespace tb
 
 extern "C" {
@@ -244,14 +354,19 @@ int tb_decay_recurrence_prep(void* stream, float* proj, int stride, const int* p
                     cols, H, dk, dv, rd, act, key_scale);
 }
 
-// state float32 [slots, H, dk, dv]; out float32 [T, H dv]; cu_seqlens [requests + 1]; state_slots [requests].
-int tb_decay_recurrence_scan(void* stream, const float* proj, int stride, const int* cu_seqlens, const int* state_slots,
-                             float* state, const float* decay, float* out, int requests, int H, int dk, int dv) {
+// The scan with everything as an argument.  state float32: slot s begins at state + s * state_stride and holds
+// [H, dk, dv]; out float32 [T, H dv]; cu_seqlens [requests + 1]; state_slots [requests]; decay [H] or null (1);
+// decay_tok [T, H] or null; q of set i at column q_off + i dk, k at k_off + i dk, v of head h at v_off + h dv.
+int tb_recurrence_scan(void* stream, const float* proj, int stride, const int* cu_seqlens, const int* state_slots,
+                       float* state, long long state_stride, const float* decay, const float* decay_tok, float* out, int requests,
+                       int H, int qk_heads, int dk, int dv, int q_off, int k_off, int v_off) {
   if (requests <= 0) return 0;
-  if (H <= 0 || dk <= 0 || dk > 1024 || dv <= 0 || H > 65535 || requests > 65535) return TB_ERR_BAD_SIZE;
+  if (H <= 0 || dk <= 0 || dk > 1024 || dv <= 0 || H > 65535 || requests > 65535 || qk_heads <= 0 || H % qk_heads ||
+      state_stride < (long long)H * dk * dv || q_off < 0 || k_off < 0 || v_off < 0)
+    return TB_ERR_BAD_SIZE;
   const int R = dk <= 512 ? 16 : 32;
   const int nw = (dk + R - 1) / R, dkp = nw * R;
-  const size_t smem = (size_t)(2 * (2 * tb::DR_CHUNK * dkp + tb::DR_CHUNK * 32) + tb::DR_CHUNK * nw * 32) * sizeof(float);
+  const size_t smem = (size_t)(2 * (2 * tb::DR_CHUNK * dkp + tb::DR_CHUNK * 32 + tb::DR_CHUNK) + tb::DR_CHUNK * nw * 32) * sizeof(float);
   auto kernel = dk <= 256 ? tb::decay_recurrence_scan_kernel
                           : (R == 16 ? tb::decay_recurrence_scan_wide_kernel<16> : tb::decay_recurrence_scan_wide_kernel<32>);
   if (smem > 48 * 1024) {
@@ -259,7 +374,46 @@ int tb_decay_recurrence_scan(void* stream, const float* proj, int stride, const 
     if (e != cudaSuccess) return (int)e;
   }
   return tb::launch(kernel, dim3((dv + 31) / 32, H, requests), dim3(nw * 32), smem, stream, proj, stride, cu_seqlens, state_slots,
-                    state, decay, out, H, dk, dv);
+                    state, decay, out, H, dk, dv, decay_tok, qk_heads, q_off, k_off, v_off, state_stride);
+}
+
+// The fixed-decay layout: columns [q: H dk | k: H dk | v: H dv], state float32 [slots, H, dk, dv].
+int tb_decay_recurrence_scan(void* stream, const float* proj, int stride, const int* cu_seqlens, const int* state_slots,
+                             float* state, const float* decay, float* out, int requests, int H, int dk, int dv) {
+  return tb_recurrence_scan(stream, proj, stride, cu_seqlens, state_slots, state, (long long)H * dk * dv, decay, nullptr, out,
+                            requests, H, H, dk, dv, 0, H * dk, 2 * H * dk);
+}
+
+// proj float32 [T, stride >= 2 H P + GN2 + H]; taps [H P + GN2, K]; conv_state: slot s at conv_state + s * state_stride,
+// [K - 1][H P + GN2]; rows float32 [T, 2 H P + GN2] = [x | B | C | dt x]; decay float32 [T, H].
+int tb_selective_prep(void* stream, const float* proj, int stride, const float* taps, const float* conv_bias, const float* dt_bias,
+                      const float* a_log, const float* conv_state, long long state_stride, const int* seq_of_token,
+                      const int* positions, const int* seq_starts, const int* state_slots, float* rows, float* decay, int T_tokens,
+                      int H, int P, int GN2, int K) {
+  if (T_tokens <= 0) return 0;
+  if (H <= 0 || P <= 0 || GN2 < 0 || K <= 0 || stride < 2 * H * P + GN2 + H) return TB_ERR_BAD_SIZE;
+  const long long total = (long long)T_tokens * (H * P + GN2);
+  long long blocks = (total + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  return tb::launch(tb::selective_prep_kernel, dim3((int)blocks), dim3(256), 0, stream, proj, stride, taps, conv_bias, dt_bias, a_log,
+                    conv_state, state_stride, seq_of_token, positions, seq_starts, state_slots, rows, decay, total, H, P, GN2, K);
+}
+
+int tb_conv_state_update(void* stream, const float* proj, int stride, int col0, float* conv_state, long long state_stride,
+                         const int* cu_seqlens, const int* state_slots, int requests, int C, int K) {
+  if (requests <= 0 || K <= 1) return 0;
+  if (C <= 0 || col0 < 0) return TB_ERR_BAD_SIZE;
+  const long long total = (long long)requests * C;
+  return tb::launch(tb::conv_state_update_kernel, dim3((int)((total + 255) / 256)), dim3(256), 0, stream, proj, stride, col0,
+                    conv_state, state_stride, cu_seqlens, state_slots, requests, C, K);
+}
+
+int tb_selective_post(void* stream, const float* o, const float* rows, int rows_stride, const float* z, int z_stride, const float* D,
+                      const float* weight, void* y, int T_tokens, int H, int P, int parts, float eps, int dtype) {
+  if (T_tokens <= 0) return 0;
+  if (H <= 0 || P <= 0 || parts <= 0 || (H * P) % parts || parts > 65535) return TB_ERR_BAD_SIZE;
+  TB_DISPATCH_DTYPE(dtype, tb::launch(tb::selective_post_kernel<T>, dim3(T_tokens, parts), dim3(256), 0, stream, o, rows, rows_stride,
+                                      z, z_stride, D, weight, (T*)y, H, P, parts, eps));
 }
 
 // o float32 [T, H dv]; gate float32 rows of H dv values (stride gate_stride) or null; weight [H dv] or null (mode 1).

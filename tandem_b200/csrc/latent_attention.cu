@@ -1,0 +1,174 @@
+// Attention over a cached latent: what surrounds the attention kernel.
+//
+// A token stores c = RMSNorm(first R numbers of its down-projection) * w and one rotated key part
+// k_r of r numbers that all heads share.  Head h's key is [W_uk[h] c | k_r] and its value W_uv[h] c, so
+//
+//   score_h(i, j) = (q_h(i) . W_uk[h] c_j + q_r,h(i) . k_r(j)) * scale = ([W_uk[h]^T q_h(i) | q_r,h(i)] . [c_j | k_r(j)]) * scale
+//   o_h(i) = W_uv[h] sum_j p_h(i, j) c_j
+//
+// which is attention of H query heads of R + r numbers over ONE key head [c | k_r] whose values are c:
+// nothing per head is ever expanded for a cached token.  `latent_prep` makes the cache entry of each
+// new token (norm, rotation, write into the paged key cache rows [c | k_r] and value cache rows c) and
+// rotates the rotated part of every query head in place; `head_linear` is the small product per head
+// that folds W_uk into the queries in front of the attention kernel and applies W_uv behind it.
+// The attention itself is the package's kernel for keys and values of different sizes.
+// Rotation: rotate_half pairing (i, i + rd/2) of the first rd numbers of the rotated part, angle =
+// position * freq[i] in float32.  All arithmetic float32; T is the storage type of the cache.
+#include "cache_layout.cuh"
+#include "common.cuh"
+
+namespace tb {
+
+// One block per token.  proj float32 [T, stride]: H query heads of (d + r) numbers from column 0, the
+// down-projection (R + r numbers) from column kv_col.  q_out float32 [T, H, R + r]: the rotated query part
+// is written to columns R .. R + r of each head (the first R columns are filled by head_linear).
+template <typename T>
+__global__ void latent_prep_kernel(const float* __restrict__ proj, int stride, int kv_col, const float* __restrict__ norm_w,
+                                   const float* __restrict__ freq, const int* __restrict__ positions,
+                                   const int* __restrict__ slots, T* __restrict__ k_cache, T* __restrict__ v_cache,
+                                   float* __restrict__ q_out, int H, int d, int r, int rd, int R, int page_size, float eps,
+                                   int write_kv) {
+  __shared__ float scratch[33];
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x;
+  const float* row = proj + (size_t)t * stride;
+  const float pos = (float)positions[t];
+  const int half = rd >> 1;
+  // the rotated part of every query head
+  for (int e = threadIdx.x; e < H * r; e += blockDim.x) {
+    const int h = e / r, i = e % r;
+    const float* src = row + (size_t)h * (d + r) + d;
+    float v;
+    if (i < half) {
+      const float a = pos * freq[i];
+      v = src[i] * cosf(a) - src[i + half] * sinf(a);
+    } else if (i < rd) {
+      const float a = pos * freq[i - half];
+      v = src[i] * cosf(a) + src[i - half] * sinf(a);
+    } else {
+      v = src[i];
+    }
+    q_out[((size_t)t * H + h) * (R + r) + R + i] = v;
+  }
+  // the cache entry
+  const float* kv = row + kv_col;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < R; i += blockDim.x) ss = fmaf(kv[i], kv[i], ss);
+  ss = block_sum(ss, scratch);
+  const int slot = (write_kv && slots) ? slots[t] : -1;
+  if (slot < 0) return;
+  const float inv = rsqrtf(ss / (float)R + eps);
+  const int dk = R + r;
+  T* ktile = k_cache + cache_tile(slot / page_size, 0, 1, page_size, dk);
+  T* vtile = v_cache + cache_tile(slot / page_size, 0, 1, page_size, R);
+  const int rr = slot % page_size;
+  for (int i = threadIdx.x; i < R; i += blockDim.x) {
+    const T c = from_float<T>(kv[i] * inv * norm_w[i]);
+    ktile[cache_offset<T>(rr, i, page_size, dk)] = c;
+    vtile[cache_offset<T>(rr, i, page_size, R)] = c;
+  }
+  for (int i = threadIdx.x; i < r; i += blockDim.x) {
+    const float* src = kv + R;
+    float v;
+    if (i < half) {
+      const float a = pos * freq[i];
+      v = src[i] * cosf(a) - src[i + half] * sinf(a);
+    } else if (i < rd) {
+      const float a = pos * freq[i - half];
+      v = src[i] * cosf(a) + src[i - half] * sinf(a);
+    } else {
+      v = src[i];
+    }
+    ktile[cache_offset<T>(rr, R + i, page_size, dk)] = from_float<T>(v);
+  }
+}
+
+// out[t, h, n] = sum_k x[t, h, k] * W[h][n, k]  (or W[h][k, n] with `transposed`), one block per (token, head).
+// x rows: x + t * x_stride + h * x_head; out rows: out + t * out_stride + h * out_head.  X, W: float or bfloat16;
+// sums in float32 in ascending k, so a token's result does not depend on the batch.
+template <typename X, typename W, typename O>
+__global__ void head_linear_kernel(const X* __restrict__ x, long long x_stride, int x_head, const W* __restrict__ w,
+                                   O* __restrict__ out, long long out_stride, int out_head, int N, int K, int transposed) {
+  extern __shared__ float xs[];  // K floats
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x, h = blockIdx.y;
+  const X* xr = x + (size_t)t * x_stride + (size_t)h * x_head;
+  for (int k = threadIdx.x; k < K; k += blockDim.x) xs[k] = to_float(xr[k]);
+  __syncthreads();
+  const W* wh = w + (size_t)h * N * K;
+  O* o = out + (size_t)t * out_stride + (size_t)h * out_head;
+  if (transposed) {  // W[h] is [K, N]: neighbouring threads read neighbouring n
+    for (int n = threadIdx.x; n < N; n += blockDim.x) {
+      float acc = 0.f;
+      for (int k = 0; k < K; ++k) acc = fmaf(xs[k], to_float(wh[(size_t)k * N + n]), acc);
+      o[n] = from_float<O>(acc);
+    }
+    return;
+  }
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  for (int n = warp; n < N; n += nw) {  // W[h] is [N, K]: a warp per output, lanes along k
+    float acc = 0.f;
+    for (int k = lane; k < K; k += 32) acc = fmaf(xs[k], to_float(wh[(size_t)n * K + k]), acc);
+    acc = warp_sum(acc);
+    if (lane == 0) o[n] = from_float<O>(acc);
+  }
+}
+
+// y[t, c] = o[t, c] * sigmoid(g[t, c]), rounded to T.  o of type T, g float32 rows with stride g_stride.
+template <typename T>
+__global__ void sigmoid_gate_kernel(const float* __restrict__ o, const float* __restrict__ g, int g_stride, T* __restrict__ y,
+                                    long long total, int N) {
+  pdl_launch_dependents();
+  pdl_wait();
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const long long t = i / N;
+    const int c = (int)(i % N);
+    const float gate = g ? 1.f / (1.f + expf(-g[(size_t)t * g_stride + c])) : 1.f;
+    y[i] = from_float<T>(o[i] * gate);
+  }
+}
+
+}  // namespace tb
+
+extern "C" {
+
+int tb_latent_prep(void* stream, const float* proj, int stride, int kv_col, const float* norm_w, const float* freq,
+                   const int* positions, const int* slots, void* k_cache, void* v_cache, float* q_out, int T_tokens, int H, int d,
+                   int r, int rd, int R, int page_size, float eps, int write_kv, int dtype) {
+  if (T_tokens <= 0) return 0;
+  if (H <= 0 || d <= 0 || r < 0 || rd < 0 || rd > r || (rd & 1) || R <= 0 || page_size <= 0 || (rd && !freq)) return TB_ERR_BAD_SIZE;
+  TB_DISPATCH_DTYPE(dtype, tb::launch(tb::latent_prep_kernel<T>, dim3(T_tokens), dim3(128), 0, stream, proj, stride, kv_col, norm_w,
+                                      freq, positions, slots, (T*)k_cache, (T*)v_cache, q_out, H, d, r, rd, R, page_size, eps,
+                                      write_kv));
+}
+
+// x_dtype / w_dtype / out_dtype: TB_F32 or TB_BF16 (x and out float32 with either weight type; x bfloat16 with bfloat16 weights).
+int tb_head_linear(void* stream, const void* x, int x_dtype, long long x_stride, int x_head, const void* w, int w_dtype, void* out,
+                   int out_dtype, long long out_stride, int out_head, int T_tokens, int H, int N, int K, int transposed) {
+  if (T_tokens <= 0) return 0;
+  if (H <= 0 || H > 65535 || N <= 0 || K <= 0 || K > 12288) return TB_ERR_BAD_SIZE;
+  const dim3 grid(T_tokens, H), block(128);
+  const size_t smem = (size_t)K * sizeof(float);
+#define TB_HL(XX, WW, OO)                                                                                                         \
+  return tb::launch(tb::head_linear_kernel<XX, WW, OO>, grid, block, smem, stream, (const XX*)x, x_stride, x_head, (const WW*)w, \
+                    (OO*)out, out_stride, out_head, N, K, transposed)
+  using B = __nv_bfloat16;
+  if (x_dtype == TB_F32 && w_dtype == TB_F32 && out_dtype == TB_F32) TB_HL(float, float, float);
+  if (x_dtype == TB_F32 && w_dtype == TB_BF16 && out_dtype == TB_F32) TB_HL(float, B, float);
+  if (x_dtype == TB_BF16 && w_dtype == TB_BF16 && out_dtype == TB_F32) TB_HL(B, B, float);
+#undef TB_HL
+  return TB_ERR_BAD_DTYPE;
+}
+
+int tb_sigmoid_gate(void* stream, const float* o, const float* g, int g_stride, void* y, int T_tokens, int N, int dtype) {
+  const long long total = (long long)T_tokens * N;
+  if (total <= 0) return 0;
+  long long blocks = (total + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  TB_DISPATCH_DTYPE(dtype, tb::launch(tb::sigmoid_gate_kernel<T>, dim3((int)blocks), dim3(256), 0, stream, o, g, g_stride, (T*)y,
+                                      total, N));
+}
+
+}  // extern "C"

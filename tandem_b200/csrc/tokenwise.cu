@@ -13,6 +13,7 @@ namespace tb {
 // ---------------------------------------------------------------------------------------------
 // Embedding: out[t, :] = scale * float(table[ids[t], :]) (+ float(pos_table[positions[t], :]) where
 // the model has a learned table of absolute positions).  The residual stream is float32 in both modes.
+// Models that keep several residual streams get the row `copies` times: out is [T, copies, H].
 template <typename T>
 __global__ void embedding_kernel(const int* __restrict__ ids, const T* __restrict__ table,
                                  float* __restrict__ out, int H, int V, float scale, const int* __restrict__ positions,
@@ -21,7 +22,7 @@ __global__ void embedding_kernel(const int* __restrict__ ids, const T* __restric
   pdl_wait();
   const int t = blockIdx.x;
   const int id = ids[t];
-  float* o = out + (size_t)t * H;
+  float* o = out + ((size_t)t * gridDim.y + blockIdx.y) * H;  // gridDim.y copies of the row side by side
   if (id < 0 || id >= V) {  // the host checks ids; never read outside the table
     for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = 0.f;
     return;
@@ -511,10 +512,10 @@ extern "C" {
 
 // positions / pos_table [max_pos, H] may be null (no learned absolute positions).
 int tb_embedding(void* stream, const int* ids, const void* table, float* out, int T_tokens, int H, int V,
-                 int dtype, float scale, const int* positions, const void* pos_table, int max_pos) {
+                 int dtype, float scale, const int* positions, const void* pos_table, int max_pos, int copies) {
   if (T_tokens <= 0) return 0;
-  if (pos_table && (!positions || max_pos <= 0)) return TB_ERR_BAD_SIZE;
-  TB_DISPATCH_DTYPE(dtype, tb::launch(tb::embedding_kernel<T>, dim3(T_tokens), dim3(256), 0, stream, ids, (const T*)table, out, H, V,
+  if ((pos_table && (!positions || max_pos <= 0)) || copies <= 0 || copies > 65535) return TB_ERR_BAD_SIZE;
+  TB_DISPATCH_DTYPE(dtype, tb::launch(tb::embedding_kernel<T>, dim3(T_tokens, copies), dim3(256), 0, stream, ids, (const T*)table, out, H, V,
                                       scale, positions, (const T*)pos_table, max_pos));
 }
 

@@ -11,6 +11,7 @@ LIBRARIES = [
     ("attention_simt", ()),
     ("sampling", ()),
     ("sink_attention", ()), ("decay_recurrence", ()),
+    ("streams", ()), ("latent_attention", ()), ("moe", ()),
     ("gemm_skinny", ()), ("gemm_wide", ()), ("gemm_wide_pair", ()), ("gemv_bf16", ()),
 ] + [(stem, (f"TB_HD={hd}",)) for hd in (16, 32, 48, 64, 128) for stem in ("attention_decode", "attention_prefill")] \
     + [("attention_prefill_tc", (f"TB_HD={hd}",)) for hd in (64, 128)] \

@@ -19,6 +19,12 @@ that travels between the parts of a layer must be allowed to be *not computed ye
                    an output bias returns when asked, so that the arrangement adds product and bias
                    into the float32 residual in one pass, without a rounding in between.
 
+``StreamWrite``    a sublayer's output y that has still to enter a residual of several streams, with the
+                   coefficients of its link: X_t <- sum_s mix[s, t] X_s + mult * out[t] * y.  The norm in front of
+                   the next sublayer (or the model's last norm) does the write, the next read and the norm in one
+                   kernel (``ops.stream_norm``).  It stands for no tensor: only arrangements that keep such a
+                   residual hand it on.
+
 Only parts that say ``takes_deferred = True`` ever meet one of these; everything else gets tensors
 (``tensor`` computes what is pending with the stand-alone kernels).  12vivi/tandem fuses the same
 pair into its small-batch product (python/tandem/layers/triton_gemv.py:92-145,356-378).
@@ -68,8 +74,20 @@ class Unsummed:
         return tuple(self.product.shape)
 
 
+@dataclass
+class StreamWrite:
+    y: torch.Tensor  # [M, H] float32 or the model's type
+    mix: torch.Tensor  # [S, S] float32, indexed [from, to]
+    out: torch.Tensor  # [S] float32
+    mult: float
+
+    @property
+    def shape(self) -> tuple:
+        return tuple(self.y.shape)
+
+
 def is_pending(v: Any) -> bool:
-    return isinstance(v, (PendingLinear, PendingNorm, Unsummed))
+    return isinstance(v, (PendingLinear, PendingNorm, Unsummed, StreamWrite))
 
 
 def tensor(v: Any) -> Optional[torch.Tensor]:
@@ -84,4 +102,7 @@ def tensor(v: Any) -> Optional[torch.Tensor]:
         return ops.add_rmsnorm(None, v.residual, v.weight, v.eps, v.out_dtype)
     if isinstance(v, Unsummed):
         return ops.bias_act(v.product, v.bias, "none", v.out_dtype)
+    if isinstance(v, StreamWrite):
+        raise TypeError("a write into a residual of several streams stands for no tensor: the arrangement behind it must "
+                        "keep such a residual (its norm does the write)")
     raise TypeError(f"{type(v).__name__} stands for no tensor")

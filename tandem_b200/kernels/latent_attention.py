@@ -1,0 +1,79 @@
+"""Entry points of ``csrc/latent_attention.cu``: what surrounds the attention kernel when keys and
+values are expanded from a cached latent (cache entry and query rotation; the small product per
+head that folds the key expansion into the queries and applies the value expansion; the gate)."""
+
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from tandem_b200.kernels import ops
+from tandem_b200.kernels.build import load_library
+
+
+def prepare(proj: torch.Tensor, kv_col: int, norm_weight: torch.Tensor, freq: Optional[torch.Tensor], positions: torch.Tensor, kv,
+            num_heads: int, head_dim: int, rotary_dim: int, latent_dim: int, eps: float) -> torch.Tensor:
+    """proj float32 [T, cols]: ``num_heads`` query heads of head_dim + rotary_dim numbers from column 0 and the
+    down-projection (latent_dim + rotary_dim numbers) from ``kv_col``.  Writes the token's cache entry (key row
+    [RMSNorm(latent) * weight | rotated key part], value row the normed latent) and returns the queries' room
+    float32 [T, H, latent_dim + rotary_dim] with the rotated part of every head filled in."""
+    ops._need(proj, "proj", torch.float32)
+    ops._need(norm_weight, "norm weight", torch.float32)
+    ops._need(positions, "positions", torch.int32)
+    T, R, r = proj.shape[0], latent_dim, rotary_dim
+    rd = 0
+    if freq is not None:
+        ops._need(freq, "freq", torch.float32)
+        rd = 2 * freq.numel()
+    if norm_weight.numel() != R or kv_col + R + r > proj.shape[1] or num_heads * (head_dim + r) > proj.shape[1]:
+        raise ops.KernelError(f"projection of {proj.shape[1]} columns / norm weight of {norm_weight.numel()} do not fit "
+                              f"{num_heads} heads of {head_dim} + {r} and a latent of {R} + {r} at column {kv_col}")
+    if kv.writable:
+        ops._need(kv.slots, "slots", torch.int32)
+        if tuple(kv.k.shape[1:]) != (1, kv.page_size, R + r) or tuple(kv.v.shape[1:]) != (1, kv.page_size, R):
+            raise ops.KernelError(f"caches {tuple(kv.k.shape)} / {tuple(kv.v.shape)} do not fit a latent of {R} + {r}")
+    q = torch.empty((T, num_heads, R + r), dtype=torch.float32, device=proj.device)
+    lib = load_library("latent_attention")
+    ops._check(lib.tb_latent_prep(ops._stream(), ops._ptr(proj), proj.stride(0), kv_col, ops._ptr(norm_weight), ops._ptr(freq),
+                                  ops._ptr(positions), ops._ptr(kv.slots), ops._ptr(kv.k), ops._ptr(kv.v), ops._ptr(q), T, num_heads,
+                                  head_dim, r, rd, R, kv.page_size, ctypes.c_float(eps), int(bool(kv.writable)),
+                                  ops._code(kv.k.dtype)), "latent_prep")
+    return q
+
+
+def head_linear(x: torch.Tensor, x_head: int, weight: torch.Tensor, out: torch.Tensor, out_head: int, num_heads: int, n: int, k: int,
+                transposed: bool) -> None:
+    """out[t, h, :n] = W[h] x[t, h, :k] for every token and head: x rows of any stride with head h at column
+    h * x_head, likewise ``out`` (float32); ``weight`` holds W[h] as [n, k] (or [k, n] with ``transposed``),
+    head after head.  x float32 or bfloat16, weight of the model's type; sums in float32."""
+    ops._need(x, "x", contiguous=False)
+    ops._need(weight, "weight")
+    ops._need(out, "out", torch.float32, contiguous=False)
+    if weight.numel() != num_heads * n * k or x.stride(-1) != 1 or out.stride(-1) != 1:
+        raise ops.KernelError(f"weight of {weight.numel()} elements does not hold {num_heads} matrices of {n} x {k}")
+    T = x.shape[0]
+    lib = load_library("latent_attention")
+    ops._check(lib.tb_head_linear(ops._stream(), ops._ptr(x), ops._code(x.dtype), ctypes.c_longlong(x.stride(0)), x_head,
+                                  ops._ptr(weight), ops._code(weight.dtype), ops._ptr(out), ops._code(out.dtype),
+                                  ctypes.c_longlong(out.stride(0)), out_head, T, num_heads, n, k, int(bool(transposed))),
+               "head_linear")
+
+
+def sigmoid_gate(o: torch.Tensor, gate: Optional[torch.Tensor], out_dtype: torch.dtype) -> torch.Tensor:
+    """o * sigmoid(gate) for float32 o [T, N] and float32 gate rows of N values (any row stride; None: no gate),
+    rounded to ``out_dtype``."""
+    ops._need(o, "o", torch.float32)
+    T, N = o.shape
+    stride = 0
+    if gate is not None:
+        ops._need(gate, "gate", torch.float32, contiguous=False)
+        if tuple(gate.shape) != (T, N) or gate.stride(1) != 1:
+            raise ops.KernelError(f"gate {tuple(gate.shape)} does not fit o {tuple(o.shape)}")
+        stride = gate.stride(0)
+    y = torch.empty((T, N), dtype=out_dtype, device=o.device)
+    lib = load_library("latent_attention")
+    ops._check(lib.tb_sigmoid_gate(ops._stream(), ops._ptr(o), ops._ptr(gate), stride, ops._ptr(y), T, N, ops._code(out_dtype)),
+               "sigmoid_gate")
+    return y

@@ -1,0 +1,81 @@
+"""Entry points of ``csrc/moe.cu``: routing by score, and the chosen experts' gated feed-forwards.
+
+``route`` turns float32 router logits into (expert, weight) pairs.  ``experts`` runs the chosen
+experts of every token over stacked weights: one warp per output element for steps of few tokens
+and for the 32-bit path; slots sorted by expert on the device and 64 x 64 tiles on the tensor
+cores for bfloat16 steps of many tokens.  Nothing goes through the host, so the step can be
+captured in a CUDA graph.
+"""
+
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from tandem_b200.kernels import ops
+from tandem_b200.kernels.build import load_library
+
+_SCORES = {"sigmoid": 0, "softmax": 1}
+TILE_MIN_TOKENS = 33  # from here on the sorted tiles run (bfloat16): below, an expert's rows are read once per slot anyway
+_MAX_SLOTS = 65535  # slots per launch of the one-warp-per-output kernels
+
+
+def route(logits: torch.Tensor, top_k: int, score: str, normalize: bool, scale: float) -> tuple:
+    """logits float32 [T, E] -> (experts int32 [T, top_k], weights float32 [T, top_k]): scores sigmoid(z) or
+    softmax(z), the ``top_k`` largest chosen (the lower index wins a tie), their scores divided by their sum
+    (+ 1e-20) where ``normalize``, times ``scale``."""
+    ops._need(logits, "logits", torch.float32)
+    if score not in _SCORES:
+        raise ops.KernelError(f"no score {score!r} (have {sorted(_SCORES)})")
+    T, E = logits.shape
+    ids = torch.empty((T, top_k), dtype=torch.int32, device=logits.device)
+    weights = torch.empty((T, top_k), dtype=torch.float32, device=logits.device)
+    lib = load_library("moe")
+    ops._check(lib.tb_moe_route(ops._stream(), ops._ptr(logits), ops._ptr(ids), ops._ptr(weights), T, E, top_k, _SCORES[score],
+                                int(bool(normalize)), ctypes.c_float(scale)), "moe_route")
+    return ids, weights
+
+
+def tiles_apply(x: torch.Tensor, hidden: int, inner: int) -> bool:
+    return (x.dtype == torch.bfloat16 and x.shape[0] >= TILE_MIN_TOKENS and hidden % 8 == 0 and inner % 8 == 0
+            and ops.env("TANDEM_MOE", "tiles") != "simt")
+
+
+def experts(x: torch.Tensor, gate_up: torch.Tensor, down: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor) -> torch.Tensor:
+    """sum_k weights[t, k] * down[e] (SiLU(gate[e] x_t) * (up[e] x_t)) with e = ids[t, k]: float32 [T, hidden].
+    x [T, hidden]; gate_up [E, 2 F, hidden] (an expert's gate rows, then its up rows); down [E, hidden, F]."""
+    ops._need(x, "x")
+    ops._need(gate_up, "gate_up", x.dtype)
+    ops._need(down, "down", x.dtype)
+    ops._need(ids, "ids", torch.int32)
+    ops._need(weights, "weights", torch.float32)
+    T, K = x.shape
+    E, F2, K2 = gate_up.shape
+    F, top = F2 // 2, ids.shape[1]
+    if K2 != K or tuple(down.shape) != (E, K, F) or tuple(ids.shape) != (T, top) or tuple(weights.shape) != (T, top):
+        raise ops.KernelError(f"x {tuple(x.shape)}, gate_up {tuple(gate_up.shape)}, down {tuple(down.shape)}, ids "
+                              f"{tuple(ids.shape)} do not fit together")
+    y = torch.empty((T, K), dtype=torch.float32, device=x.device)
+    lib = load_library("moe")
+    if tiles_apply(x, K, F):
+        rows = lib.tb_moe_tile_rows()
+        capacity = -(-(T * top + E * (rows - 1)) // rows) * rows
+        offsets = torch.empty(E + 1, dtype=torch.int32, device=x.device)
+        order = torch.empty(capacity, dtype=torch.int32, device=x.device)
+        act = torch.empty((capacity, F), dtype=torch.bfloat16, device=x.device)
+        part = torch.empty((T * top, K), dtype=torch.float32, device=x.device)
+        ops._check(lib.tb_moe_tiles(ops._stream(), ops._ptr(x), ops._ptr(gate_up), ops._ptr(down), ops._ptr(ids), ops._ptr(weights),
+                                    ops._ptr(offsets), ops._ptr(order), ops._ptr(act), ops._ptr(part), ops._ptr(y), T, top, E, K, F, K,
+                                    capacity), "moe_tiles")
+        ops.launches += 3  # four kernels
+        return y
+    step = max(1, _MAX_SLOTS // top)
+    for t0 in range(0, T, step):
+        n = min(step, T - t0)
+        act = torch.empty((n * top, F), dtype=x.dtype, device=x.device)
+        ops._check(lib.tb_moe_gate_up(ops._stream(), ops._ptr(x[t0:]), ops._ptr(gate_up), ops._ptr(ids[t0:]), ops._ptr(act), n, top, F,
+                                      K, ops._code(x.dtype)), "moe_gate_up")
+        ops._check(lib.tb_moe_down(ops._stream(), ops._ptr(act), ops._ptr(down), ops._ptr(ids[t0:]), ops._ptr(weights[t0:]),
+                                   ops._ptr(y[t0:]), n, top, K, F, ops._code(x.dtype)), "moe_down")
+    return y

@@ -124,10 +124,10 @@ def check_status(device) -> None:
 
 # ----------------------------------------------------------------------------- token-wise
 def embedding(ids: torch.Tensor, table: torch.Tensor, scale: float = 1.0, positions: Optional[torch.Tensor] = None,
-              position_table: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """ids [T] int32, table [V, H] -> float32 [T, H] (the start of the residual stream):
-    ``scale * table[ids]``, plus ``position_table[positions]`` where a learned table [P, H] of
-    absolute positions is given."""
+              position_table: Optional[torch.Tensor] = None, copies: int = 1) -> torch.Tensor:
+    """ids [T] int32, table [V, H] -> float32 [T, copies * H] (the start of the residual stream, written
+    ``copies`` times side by side for models that keep several streams): ``scale * table[ids]``, plus
+    ``position_table[positions]`` where a learned table [P, H] of absolute positions is given."""
     _need(ids, "ids", torch.int32)
     _need(table, "embedding table")
     T, (V, H) = ids.numel(), table.shape
@@ -139,10 +139,11 @@ def embedding(ids: torch.Tensor, table: torch.Tensor, scale: float = 1.0, positi
             raise KernelError(f"position table {tuple(position_table.shape)} / {positions.numel()} positions do not fit "
                               f"{T} tokens of width {H}")
         max_pos = position_table.shape[0]
-    out = torch.empty((T, H), dtype=torch.float32, device=table.device)
+    out = torch.empty((T, copies * H), dtype=torch.float32, device=table.device)
     lib = load_library("tokenwise")
     _check(lib.tb_embedding(_stream(), _ptr(ids), _ptr(table), _ptr(out), T, H, V, _code(table.dtype), ctypes.c_float(scale),
-                            _ptr(positions if position_table is not None else None), _ptr(position_table), max_pos), "embedding")
+                            _ptr(positions if position_table is not None else None), _ptr(position_table), max_pos, int(copies)),
+           "embedding")
     return out
 
 
@@ -179,6 +180,8 @@ def add_rmsnorm(x, residual: torch.Tensor, weight: torch.Tensor, eps: float,
     its own kernel and the norm comes back with its rows' scale left to the product behind it."""
     from tandem_b200.kernels import deferred, gemm_bf16
 
+    if isinstance(x, deferred.StreamWrite):
+        return stream_norm(residual, x, None, weight, eps, out_dtype, rows)
     if isinstance(x, deferred.PendingLinear):
         if defer and rows is None and out_dtype == torch.bfloat16 and x.shape == tuple(residual.shape) \
                 and gemm_bf16.add_fusable(x.x, x.weight):
@@ -205,6 +208,44 @@ def add_rmsnorm(x, residual: torch.Tensor, weight: torch.Tensor, eps: float,
     _check(lib.tb_add_rmsnorm(_stream(), _ptr(x), _ptr(residual), _ptr(weight), _ptr(y), _ptr(rows), n, H,
                               ctypes.c_float(eps), _code(out_dtype)), "add_rmsnorm")
     return y
+
+
+def stream_norm(streams: torch.Tensor, write, read: Optional[torch.Tensor], weight: torch.Tensor, eps: float,
+                out_dtype: torch.dtype, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """A residual of S streams side by side, ``streams`` float32 [T, S H]: first the write that a sublayer left
+    pending (``write``: a ``deferred.StreamWrite`` or None; X_t <- sum_s mix[s, t] X_s + mult * out[t] * y, in place),
+    then u = sum_s read[s] X_s (``read`` None: the plain sum) and RMSNorm(u) * weight in ``out_dtype``.  With
+    ``rows`` [R] int32 only those rows are updated and returned, in that order."""
+    _need(streams, "streams", torch.float32)
+    _need(weight, "norm weight", torch.float32)
+    T, H = streams.shape[0], weight.numel()
+    if streams.shape[1] % H:
+        raise KernelError(f"rows of {streams.shape[1]} numbers are no whole number of streams of {H}")
+    S = streams.shape[1] // H
+    y = mix = out = None
+    mult = 1.0
+    if write is not None:
+        y, mix, out, mult = write.y, write.mix, write.out, write.mult
+        _need(y, "y")
+        _need(mix, "mix", torch.float32)
+        _need(out, "out", torch.float32)
+        if tuple(y.shape) != (T, H) or mix.numel() != S * S or out.numel() != S:
+            raise KernelError(f"a write of y {tuple(y.shape)}, mix {tuple(mix.shape)}, out {tuple(out.shape)} does not fit "
+                              f"{S} streams of {T} x {H}")
+    if read is not None:
+        _need(read, "read", torch.float32)
+        if read.numel() != S:
+            raise KernelError(f"{read.numel()} read coefficients for {S} streams")
+    n = T
+    if rows is not None:
+        _need(rows, "rows", torch.int32)
+        n = rows.numel()
+    u = torch.empty((n, H), dtype=out_dtype, device=streams.device)
+    lib = load_library("streams")
+    _check(lib.tb_stream_norm(_stream(), _ptr(streams), _ptr(y), _code(y.dtype) if y is not None else 0, _ptr(mix), _ptr(out),
+                              ctypes.c_float(mult), _ptr(read), _ptr(weight), _ptr(u), _ptr(rows), n, S, H, ctypes.c_float(eps),
+                              _code(out_dtype)), "stream_norm")
+    return u
 
 
 def qk_norm_rope_kv(qkv: torch.Tensor, positions: torch.Tensor, slots: Optional[torch.Tensor],

@@ -119,7 +119,7 @@ class Decoder:
         if ctx.num_tokens == 0:
             return torch.empty((0, h.vocab_size), dtype=torch.float32, device=self.device)
         residual = ops.embedding(ctx.token_ids, self.embedding, scale=e.scale, positions=ctx.positions,
-                                 position_table=self.positions)
+                                 position_table=self.positions, copies=e.copies)
         x = None
         for r, run in enumerate(self.plan.order):
             ctx.run = r

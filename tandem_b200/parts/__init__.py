@@ -1,10 +1,12 @@
 """The built-in parts, registered by kind."""
 
 from tandem_b200.parts.attention import PagedAttention
-from tandem_b200.parts.block import ParallelBlock, PreNormBlock
-from tandem_b200.parts.mlp import DenseMLP, GatedMLP
+from tandem_b200.parts.block import ConnectedBlock, ParallelBlock, PreNormBlock
+from tandem_b200.parts.connection import StreamLink
+from tandem_b200.parts.latent_attention import LatentAttention
+from tandem_b200.parts.mlp import DenseMLP, GatedMLP, RoutedMLP
 from tandem_b200.parts.norm import RMSNorm
-from tandem_b200.parts.recurrence import DecayRecurrence
+from tandem_b200.parts.recurrence import DecayRecurrence, SelectiveRecurrence
 from tandem_b200.parts.rope import NoPosition, RotaryTable
 from tandem_b200.parts.sink_attention import SinkAttention
 from tandem_b200.registry import register_part
@@ -19,3 +21,8 @@ register_part("mixer", "sink_attention", SinkAttention)
 register_part("mixer", "decay_recurrence", DecayRecurrence)
 register_part("feed_forward", "dense_mlp", DenseMLP)
 register_part("block", "parallel", ParallelBlock)
+register_part("mixer", "selective_recurrence", SelectiveRecurrence)
+register_part("mixer", "latent_attention", LatentAttention)
+register_part("feed_forward", "routed_mlp", RoutedMLP)
+register_part("connection", "stream_link", StreamLink)
+register_part("block", "connected", ConnectedBlock)

@@ -8,6 +8,11 @@ normalise" is one kernel (12vivi/tandem python/tandem/models/llama_family.py:11-
 its output, and their outputs (with their biases) are added into the float32 stream together.
 The feed-forward may be absent.
 
+"connected": pre-norm sublayers on a residual of one or several streams, each sublayer tied to it
+by a link of its own (``parts/connection.py``): u = norm(read of the streams); y = sublayer(u);
+the streams are rewritten from themselves and y.  The write is left pending and done by the next
+norm's kernel, so every "write, read, normalise" is one launch.  The feed-forward may be absent.
+
 An arrangement declares the parts it works with as ``slots`` (slot name -> family; all needed)
 and ``optional_slots``; the decoder builds what the layer's spec lists under those names and
 hands the arrangement a layer whose attributes they are.  ``forward(layer, x, residual, ctx)``
@@ -81,3 +86,20 @@ class ParallelBlock:
             f, f_bias = self._terms(run(layer.feed_forward, h, ctx), ctx)
         ops.add_pair(residual, a, a_bias, f, f_bias)
         return None  # everything is in the stream already
+
+
+class ConnectedBlock:
+    slots = {"mixer_norm": "norm", "mixer": "mixer", "mixer_link": "connection"}
+    optional_slots = {"feed_forward_norm": "norm", "feed_forward": "feed_forward", "feed_forward_link": "connection"}
+    takes_deferred = True  # x is None or the write that the layer in front left pending
+
+    def forward(self, layer, x, residual: torch.Tensor, ctx: StepContext):
+        if x is not None and not isinstance(x, deferred.StreamWrite):
+            raise TypeError("a connected layer follows only layers of its kind: what comes in must be a pending write "
+                            "into the streams")
+        h = layer.mixer_norm.forward(x, residual, ctx.dtype, read=layer.mixer_link.read)
+        x = layer.mixer_link.write(deferred.tensor(layer.mixer.forward(h, ctx)))
+        if getattr(layer, "feed_forward", None) is not None:
+            h = layer.feed_forward_norm.forward(x, residual, ctx.dtype, read=layer.feed_forward_link.read)
+            x = layer.feed_forward_link.write(deferred.tensor(layer.feed_forward.forward(h, ctx)))
+        return x

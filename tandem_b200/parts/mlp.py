@@ -7,7 +7,7 @@ from __future__ import annotations
 import torch
 
 from tandem_b200.config.model_config import ConfigError
-from tandem_b200.config.plan import DenseMLPSpec, GatedMLPSpec, ParamSpec, WeightSource
+from tandem_b200.config.plan import DenseMLPSpec, GatedMLPSpec, ParamSpec, RoutedMLPSpec, WeightSource
 from tandem_b200.kernels import deferred, ops
 from tandem_b200.parts.base import FeedForward, StepContext
 
@@ -15,13 +15,15 @@ from tandem_b200.parts.base import FeedForward, StepContext
 class GatedMLP(FeedForward):
     takes_deferred = True  # x may be a norm whose scale is pending; with ``defer`` the last product may stay pending
 
-    @staticmethod
-    def params(spec: GatedMLPSpec) -> dict:
+    _SUFFIX = {"gate": "gate_proj.weight", "up": "up_proj.weight", "down": "down_proj.weight"}
+
+    @classmethod
+    def params(cls, spec: GatedMLPSpec) -> dict:
         H, I, p = spec.hidden_size, spec.intermediate_size, spec.prefix
+        name = {local: f"{p}.{dict(spec.names).get(local, suffix)}" for local, suffix in cls._SUFFIX.items()}
         return {
-            "gate_up": ParamSpec((2 * I, H), (WeightSource(f"{p}.gate_proj.weight", 0, I),
-                                              WeightSource(f"{p}.up_proj.weight", I, I))),
-            "down": ParamSpec((H, I), (WeightSource(f"{p}.down_proj.weight"),)),
+            "gate_up": ParamSpec((2 * I, H), (WeightSource(name["gate"], 0, I), WeightSource(name["up"], I, I))),
+            "down": ParamSpec((H, I), (WeightSource(name["down"]),)),
         }
 
     def __init__(self, spec: GatedMLPSpec, weights: dict, dtype: torch.dtype, device) -> None:
@@ -29,8 +31,11 @@ class GatedMLP(FeedForward):
             raise ConfigError(f"gated_mlp has no activation {spec.activation!r} (only silu)")
         self.gate_up = weights["gate_up"]
         self.down = weights["down"]
+        self.float32_output = spec.float32_output
 
     def forward(self, x, ctx: StepContext, defer: bool = False):
+        if self.float32_output:
+            return ops.linear(ops.gated_linear(x, self.gate_up), self.down, out_dtype=torch.float32)
         return ops.linear(ops.gated_linear(x, self.gate_up), self.down, defer=defer)
 
 
@@ -69,3 +74,42 @@ class DenseMLP(FeedForward):
         if defer:
             return deferred.Unsummed(y, self.down_bias, ctx.dtype)
         return ops.bias_act(y, self.down_bias, "none", ctx.dtype)
+
+
+class RoutedMLP(FeedForward):
+    """Experts chosen by a router (see :class:`~tandem_b200.config.plan.RoutedMLPSpec`).  The router's logits
+    come from the package's product in float32; one kernel scores and chooses; the experts' weights are held
+    stacked ([E, 2 F, H] with an expert's gate rows in front of its up rows, [E, H, F]) and run by the
+    kernels of ``csrc/moe.cu``.  Returns float32."""
+
+    @staticmethod
+    def params(spec: RoutedMLPSpec) -> dict:
+        H, F, E, p = spec.hidden_size, spec.intermediate_size, spec.num_experts, spec.prefix
+        gate_up, down = [], []
+        for e in range(E):
+            gate_up += [WeightSource(f"{p}.e{e}.gate", 2 * F * e, F), WeightSource(f"{p}.e{e}.up", 2 * F * e + F, F)]
+            down.append(WeightSource(f"{p}.e{e}.down", H * e, H))
+        return {"router": ParamSpec((E, H), (WeightSource(f"{p}.router"),)),
+                "gate_up": ParamSpec((2 * F * E, H), tuple(gate_up)), "down": ParamSpec((H * E, F), tuple(down))}
+
+    def __init__(self, spec: RoutedMLPSpec, weights: dict, dtype: torch.dtype, device) -> None:
+        if spec.activation != "silu":
+            raise ConfigError(f"routed_mlp has no activation {spec.activation!r} (only silu)")
+        if spec.score not in ("sigmoid", "softmax"):
+            raise ConfigError(f"routed_mlp has no score {spec.score!r} (sigmoid or softmax)")
+        if not 1 <= spec.top_k <= min(32, spec.num_experts):
+            raise ConfigError(f"{spec.top_k} of {spec.num_experts} experts: a token uses 1 to 32 of them")
+        self.spec = spec
+        H, F, E = spec.hidden_size, spec.intermediate_size, spec.num_experts
+        self.router = weights["router"]
+        self.gate_up = weights["gate_up"].view(E, 2 * F, H)
+        self.down = weights["down"].view(E, H, F)
+
+    def forward(self, x, ctx: StepContext, defer: bool = False):
+        from tandem_b200.kernels import moe
+
+        s = self.spec
+        x = deferred.tensor(x)
+        logits = ops.linear(x, self.router, out_dtype=torch.float32)
+        ids, weights = moe.route(logits, s.top_k, s.score, s.normalize, s.route_scale)
+        return moe.experts(x, self.gate_up, self.down, ids, weights)

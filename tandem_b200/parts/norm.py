@@ -28,5 +28,9 @@ class RMSNorm(Norm):
         self.weight = weights["weight"]
 
     def forward(self, x, residual: torch.Tensor, out_dtype: torch.dtype, rows: Optional[torch.Tensor] = None,
-                defer: bool = False):
+                defer: bool = False, read: Optional[torch.Tensor] = None):
+        """``read``: the residual is several streams side by side and the norm's input is their sum weighted by
+        these coefficients; ``x`` is then None or the write into the streams that is still pending."""
+        if read is not None:
+            return ops.stream_norm(residual, x, read, self.weight, self.eps, out_dtype, rows)
         return ops.add_rmsnorm(x, residual, self.weight, self.eps, out_dtype, rows, defer=defer)

@@ -1,4 +1,8 @@
-"""Linear attention with a fixed decay per head, as a mixer with per-request state.
+"""Recurrences with per-request state as mixers: linear attention with a fixed decay per head
+(``DecayRecurrence``) and the selective state-space layer whose decay comes from the token
+(``SelectiveRecurrence``); both run the same scan kernel.
+
+Linear attention with a fixed decay per head:
 
 S <- decay_h S + k v^T and o = S^T q per head, the state [heads, key_dim, value_dim] in float32 in
 the cache manager's state slots (zero when a request is admitted, carried from step to step).  What
@@ -12,7 +16,7 @@ from __future__ import annotations
 import torch
 
 from tandem_b200.config.model_config import ConfigError
-from tandem_b200.config.plan import DecayRecurrenceSpec, ParamSpec, WeightSource
+from tandem_b200.config.plan import DecayRecurrenceSpec, ParamSpec, SelectiveRecurrenceSpec, WeightSource
 from tandem_b200.kernels import deferred, ops
 from tandem_b200.kernels import recurrence as kernels
 from tandem_b200.parts.base import Mixer, StateNeed, StepContext
@@ -77,3 +81,76 @@ class DecayRecurrence(Mixer):
         if defer:
             return deferred.Unsummed(out, None, ctx.dtype)
         return out if ctx.dtype == torch.float32 else ops.bias_act(out, None, "none", ctx.dtype)
+
+
+class SelectiveRecurrence(Mixer):
+    """A state-space recurrence whose decay and step size come from the token (see
+    :class:`~tandem_b200.config.plan.SelectiveRecurrenceSpec`).  One projection with a float32 result;
+    one kernel runs the causal convolution (its earlier inputs from the request's state), SiLU, the
+    softplus of the step size and the decay; the scan is the package's recurrence kernel with a decay per
+    token and q and k shared by groups of heads; one kernel adds the skip term, gates, normalises in
+    equal parts and rounds.  A request's state row holds S [H, N, P] and behind it the convolution's
+    last inputs [taps - 1, channels], both float32."""
+
+    capturable = True  # forward only launches kernels; requests and their state rows are read from device arrays
+    capturable_portions = True
+    _SUFFIX = {"in": "in", "conv": "conv", "conv_bias": "conv.b", "dt_bias": "dt_bias", "a_log": "A_log", "skip": "D",
+               "norm": "norm", "o": "o"}
+
+    @classmethod
+    def _name(cls, spec, local: str) -> str:
+        return f"{spec.prefix}.{dict(spec.names).get(local, cls._SUFFIX[local])}"
+
+    @staticmethod
+    def sizes(spec: SelectiveRecurrenceSpec) -> tuple:
+        """(inner, columns of B and C together, convolution channels)."""
+        inner, gn2 = spec.num_heads * spec.value_dim, 2 * spec.groups * spec.state_dim
+        return inner, gn2, inner + gn2
+
+    @classmethod
+    def params(cls, spec: SelectiveRecurrenceSpec) -> dict:
+        inner, gn2, channels = cls.sizes(spec)
+        H = spec.num_heads
+
+        def vector(local: str, *shape) -> ParamSpec:
+            return ParamSpec(tuple(shape), (WeightSource(cls._name(spec, local)),), role="vector")
+
+        return {
+            "in": ParamSpec((inner + channels + H, spec.hidden_size), (WeightSource(cls._name(spec, "in")),)),
+            "conv": vector("conv", channels, spec.conv_taps), "conv_bias": vector("conv_bias", channels),
+            "dt_bias": vector("dt_bias", H), "a_log": vector("a_log", H), "skip": vector("skip", H),
+            "norm": vector("norm", inner),
+            "o": ParamSpec((spec.hidden_size, inner), (WeightSource(cls._name(spec, "o")),)),
+        }
+
+    @classmethod
+    def state_need(cls, spec: SelectiveRecurrenceSpec) -> StateNeed:
+        inner, _, channels = cls.sizes(spec)
+        return StateNeed((inner * spec.state_dim + (spec.conv_taps - 1) * channels,), torch.float32)
+
+    def __init__(self, spec: SelectiveRecurrenceSpec, weights: dict, dtype: torch.dtype, device) -> None:
+        if spec.groups <= 0 or spec.num_heads % spec.groups:
+            raise ConfigError(f"{spec.num_heads} heads cannot share {spec.groups} groups of B and C")
+        if spec.norm_groups <= 0 or (spec.num_heads * spec.value_dim) % spec.norm_groups:
+            raise ConfigError(f"{spec.norm_groups} parts do not divide a row of {spec.num_heads * spec.value_dim}")
+        if spec.conv_taps <= 0:
+            raise ConfigError("the convolution needs at least the current token's tap")
+        self.spec = spec
+        self.w = weights
+
+    def forward(self, x, ctx: StepContext, defer: bool = False):
+        s, w = self.spec, self.w
+        inner, gn2, channels = self.sizes(s)
+        x = deferred.tensor(x)
+        proj = ops.linear(x, w["in"], out_dtype=torch.float32)
+        state = ctx.state(self)
+        conv_offset = inner * s.state_dim
+        rows, decay = kernels.selective_prepare(proj, w["conv"], w["conv_bias"], w["dt_bias"], w["a_log"], state, conv_offset, ctx,
+                                                s.num_heads, s.value_dim, gn2, s.conv_taps)
+        kernels.conv_state_update(proj, inner, state, conv_offset, ctx, channels, s.conv_taps)
+        # rows = [x | B | C | dt x]: q = C, k = B, v = dt x
+        o = kernels.scan_general(rows, ctx.cu_seqlens, ctx.state_slots, ctx.num_seqs, state, None, decay, s.num_heads, s.groups,
+                                 s.state_dim, s.value_dim, inner + gn2 // 2, inner, inner + gn2)
+        y = kernels.selective_finish(o, rows, proj, w["skip"], w["norm"], s.num_heads, s.value_dim, s.norm_groups, s.norm_eps,
+                                     ctx.dtype)
+        return ops.linear(y, w["o"], out_dtype=torch.float32)

@@ -28,7 +28,7 @@ class Architecture:
 
 _ARCHITECTURES: dict[str, Architecture] = {}
 _MODEL_TYPES: dict[str, str] = {}
-_PARTS: dict[str, dict[str, Any]] = {"mixer": {}, "feed_forward": {}, "norm": {}, "position": {}, "block": {}}
+_PARTS: dict[str, dict[str, Any]] = {"mixer": {}, "feed_forward": {}, "norm": {}, "position": {}, "block": {}, "connection": {}}
 
 
 def register_architecture(arch: Architecture, model_types: tuple = ()) -> None:
@@ -57,7 +57,7 @@ def supported_architectures() -> list[str]:
 
 
 def register_part(family: str, kind: str, implementation: Any) -> None:
-    """family: "mixer" | "feed_forward" | "norm" | "position" | "block"."""
+    """family: "mixer" | "feed_forward" | "norm" | "position" | "block" | "connection"."""
     if family not in _PARTS:
         raise KeyError(f"unknown part family {family!r} (have {sorted(_PARTS)})")
     _PARTS[family][kind] = implementation
@@ -81,5 +81,6 @@ def _load_builtin() -> None:
         return
     _loaded = True
     import tandem_b200.models.fumanex  # noqa: F401
+    import tandem_b200.models.kamelorn  # noqa: F401
     import tandem_b200.models.qwen3  # noqa: F401
     import tandem_b200.parts  # noqa: F401
