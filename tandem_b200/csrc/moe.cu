@@ -1,7 +1,7 @@
 // Routed experts: a token's router scores pick `top` of E small gated feed-forwards.
 //
 //   z = W_router x (float32, computed by the caller);  s = sigmoid(z)  (or softmax(z))
-//   chosen = the `top` largest s (the lower index wins a tie);  w_k = s_k / (sum of the chosen s + 1e-20) * scale
+//   chosen = the `top` largest s, found as the `top` largest z (the lower index wins a tie);  w_k = s_k / (sum of the chosen s + 1e-20) * scale
 //   y = sum_k w_k * W_down[e_k] (SiLU(W_gate[e_k] x) * (W_up[e_k] x))
 //
 // `route` takes the logits to (expert, weight) pairs, one warp per token.  A (token, k) pair is a *slot*.
@@ -33,16 +33,15 @@ route_kernel(const float* __restrict__ logits, int* __restrict__ ids, float* __r
   if (t >= T_tokens) return;
   float* s = smem + warp * E;
   const float* z = logits + (size_t)t * E;
+  // Both scores grow with the logit, so the choice is made on the logits: scores that round to the same number
+  // (a sigmoid near one) are still told apart.
+  float m = -INFINITY, sum = 1.f;
+  for (int e = lane; e < E; e += 32) { s[e] = z[e]; m = fmaxf(m, z[e]); }
   if (score == 1) {
-    float m = -INFINITY;
-    for (int e = lane; e < E; e += 32) m = fmaxf(m, z[e]);
     m = warp_max(m);
-    float sum = 0.f;
-    for (int e = lane; e < E; e += 32) { const float p = expf(z[e] - m); s[e] = p; sum += p; }
+    sum = 0.f;
+    for (int e = lane; e < E; e += 32) sum += expf(z[e] - m);
     sum = warp_sum(sum);
-    for (int e = lane; e < E; e += 32) s[e] /= sum;
-  } else {
-    for (int e = lane; e < E; e += 32) s[e] = 1.f / (1.f + expf(-z[e]));
   }
   __syncwarp();
   float total = 0.f;
@@ -57,12 +56,13 @@ route_kernel(const float* __restrict__ logits, int* __restrict__ ids, float* __r
       const int oa = __shfl_xor_sync(0xffffffffu, at, o);
       if (ob > best || (ob == best && oa < at)) { best = ob; at = oa; }
     }
+    const float sc = score == 1 ? expf(best - m) / sum : 1.f / (1.f + expf(-best));
     if (lane == 0) {
       ids[(size_t)t * top + k] = at;
-      weights[(size_t)t * top + k] = best;
+      weights[(size_t)t * top + k] = sc;
       s[at] = -INFINITY;
     }
-    total += best;
+    total += sc;
     __syncwarp();
   }
   if (lane < top) {

@@ -129,8 +129,8 @@ def tensor_shapes(cfg: KamelornConfig) -> dict:
 def random_weights(cfg: KamelornConfig, seed: int, device: str = "cpu", dtype: torch.dtype = torch.bfloat16,
                    std: float = 0.02, norm_spread: float = 0.1) -> Iterator[tuple]:
     """Seeded random tensors by checkpoint name, each from a generator of its own: matrices N(0, std)
-    (the embedding N(0, 1 / embedding scale), so the streams start near unit size; the router N(0, 25 std), so that
-    scores spread), norm weights and D 1 + U(-spread, spread), convolution taps N(0, 0.4) with biases N(0, 0.1),
+    (the embedding N(0, 1 / embedding scale), so the streams start near unit size; the router N(0, 1.5 / sqrt(width)), so that
+    scores spread without saturating), norm weights and D 1 + U(-spread, spread), convolution taps N(0, 0.4) with biases N(0, 0.1),
     dt_bias U(-4, -1), A_log U(-1, 1.5), stream reads 1 / streams + N(0, 0.1), stream writes 1 + N(0, 0.2), stream
     mixing the identity + N(0, 0.1)."""
     for index, (name, shape) in enumerate(tensor_shapes(cfg).items()):
@@ -159,7 +159,7 @@ def random_weights(cfg: KamelornConfig, seed: int, device: str = "cpu", dtype: t
             t = normal(1.0 / s, 0.1) if leaf == "in" else normal(1.0, 0.2) if leaf == "out" else \
                 torch.eye(s, device=device, dtype=torch.float32) + normal(0.0, 0.1)
         elif leaf == "router":
-            t = normal(0.0, 25.0 * std)
+            t = normal(0.0, 1.5 / cfg.width ** 0.5)
         elif name == "embed":
             t = normal(0.0, 1.0 / max(cfg.embedding_scale, 1e-6))
         else:
