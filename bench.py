@@ -2,7 +2,7 @@
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--layers L] [--impl reference]
                     [--shape 8b|14b|32b] [--prompt-len P] [--new-tokens T] [--workload decode|mixed]
-                    [--design fumanex]
+                    [--design fumanex|kamelorn]
 
 The model has the layer sizes of Qwen3-8B with seeded random weights made on the device; prompts
 are seeded random token ids.  A step is one decode step of ``--batch`` requests whose prompts
@@ -21,7 +21,9 @@ wall-clock time (benchmarks/bench_offline.py:64-86 of 12vivi/tandem).
 
 ``--design fumanex`` prints a line of its own: prefill and decode throughput of Fumanex models with
 random weights at two sizes beside Qwen3 models of equal width, heads, layers and feed-forward
-weights, and the design's own kernels against their rooflines.  The default line is untouched.
+weights, and the design's own kernels against their rooflines.  ``--design kamelorn`` does the same for Kamelorn
+models (state-space layers, attention over a cached latent, dense and routed feed-forwards, a residual of two
+streams).  The default line is untouched.
 """
 
 from __future__ import annotations
@@ -326,6 +328,92 @@ DESIGN_SIZES = {
 }
 
 
+def kamelorn_shape(width: int, heads: int, ff: int, layers: int, experts: int, top: int, expert_ff: int, groups: int) -> dict:
+    """Three state-space layers to one layer of attention over a latent; dense and routed feed-forwards in turn; a residual
+    of two streams.  State-space: inner width twice the model's in heads of 64, 128 state rows, four taps.  Latent: 96
+    numbers + 32 rotated, heads of 64 + 32 query dims and 64 value dims (the sizes the tensor-core tile kernel takes)."""
+    def mamba(mlp):
+        return dict(type="mamba2", mixer=dict(heads=2 * width // 64, vdim=64, state=128, groups=groups, conv=4, norm_groups=1), mlp=mlp)
+
+    def latent(mlp):
+        return dict(type="latent_attention", mixer=dict(heads=heads, dim=64, rot_dim=32, vdim=64, kv_rank=96, scale=96 ** -0.5,
+                                                        rot=dict(dims=32, base=1e6)), mlp=mlp)
+
+    dense = dict(kind="dense", ff=ff)
+    routed = dict(kind="moe", expert=dict(ff=expert_ff), router=dict(experts=experts, top=top, scale=1.0))
+    four = [mamba(dense), mamba(routed), latent(dense), mamba(routed)]
+    return dict(architecture="Kamelorn", vocab=151936, width=width, embedding=dict(scale=1.0), norm=dict(eps=1e-6), residual_mult=1.0,
+                streams=2, layers=[four[i % 4] for i in range(layers)])
+
+
+KAMELORN_SIZES = {
+    "2k": (kamelorn_shape(2048, 16, 5504, 8, 16, 2, 1408, 1), dict(QWEN3_8B, num_hidden_layers=8, hidden_size=2048, num_attention_heads=16,
+                                                                  num_key_value_heads=4, intermediate_size=5504)),
+    "4k": (kamelorn_shape(4096, 32, 12288, 8, 32, 4, 2048, 8), dict(QWEN3_8B, num_hidden_layers=8)),
+}
+
+
+def main_kamelorn(args) -> int:
+    import gc
+
+    import torch
+
+    from tandem_b200.kernels import microbench
+
+    pk = peaks()
+    sampler = ClockSampler()
+    sampler.start()
+    sizes = {}
+    launches = 0
+    for size, (kam, qwen) in KAMELORN_SIZES.items():
+        row = {}
+        for name, config in (("kamelorn", kam), ("qwen3", qwen)):
+            eng = design_engine(config, args.batch, PROMPT + NEW_TOKENS + args.steps + 2 * args.warmup + 32)
+            d = measure_decode(eng, args.batch, args.steps, args.warmup, PROMPT, NEW_TOKENS)
+            ms = design_prefill_ms(eng, args.warmup)
+            row[name] = {"prefill_tok_s": round(PROMPT * 1000.0 / ms, 1), "prefill_ms": round(ms, 3), "decode_tok_s": round(d["tok_s"], 1),
+                         "decode_ms_per_step": round(d["ms"], 4), "decode_e2e_tok_s": round(d["e2e_tok_s"], 1),
+                         "launches_per_decode_step": int(d["launches"]), "parameters": eng.decoder.num_parameters}
+            launches += int(d["launches"]) * args.steps
+            del eng, d
+            gc.collect()
+            torch.cuda.empty_cache()
+        sizes[size] = row
+    with torch.inference_mode():
+        sel = microbench.selective_case(PROMPT, args.batch, 128, 8, 128, 64, 20, True)
+        rec = microbench.recurrence_case(PROMPT, args.batch, 32, 128, 128, 20, True)
+        att = microbench.sink_attention_case(PROMPT, args.batch, PROMPT, 32, 1, 128, 96, PAGE, None, 0, 20, True)
+        exp = microbench.experts_case(PROMPT, args.batch, 4096, 2048, 32, 4, 20, True)
+    kernels = {
+        "selective_scan_prompt_2048": {"us": round(sel["prefill_us"], 1), "tflops_fp32": round(sel["prefill_tflops"], 2)},
+        "selective_scan_decode_b%d" % args.batch: {"us": round(sel["decode_us"], 1), "gbs": round(sel["decode_gbs"], 1),
+                                                   "frac_of_hbm": round(sel["decode_gbs"] / pk["hbm_gbs"], 4)},
+        "decay_recurrence_prompt_2048": {"us": round(rec["prefill_us"], 1), "tflops_fp32": round(rec["prefill_tflops"], 2)},
+        "decay_recurrence_decode_b%d" % args.batch: {"us": round(rec["decode_us"], 1), "gbs": round(rec["decode_gbs"], 1),
+                                                     "frac_of_hbm": round(rec["decode_gbs"] / pk["hbm_gbs"], 4)},
+        "latent_attention_tiles_prompt_2048": {"us": round(att["prefill_us"], 1), "tflops": round(att["prefill_tflops"], 1),
+                                               "frac_of_bf16_peak": round(att["prefill_tflops"] / pk["tflops"], 4)},
+        "latent_attention_decode_b%d" % args.batch: {"us": round(att["decode_us"], 1), "gbs": round(att["decode_gbs"], 1),
+                                                     "frac_of_hbm": round(att["decode_gbs"] / pk["hbm_gbs"], 4)},
+        "experts_tiles_2048_tokens": {"us": round(exp["prefill_us"], 1), "tflops": round(exp["prefill_tflops"], 1),
+                                      "frac_of_bf16_peak": round(exp["prefill_tflops"] / pk["tflops"], 4)},
+        "experts_decode_b%d" % args.batch: {"us": round(exp["decode_us"], 1), "gbs": round(exp["decode_gbs"], 1),
+                                            "frac_of_hbm": round(exp["decode_gbs"] / pk["hbm_gbs"], 4)},
+    }
+    clocks = sampler.stop()
+    k4 = sizes["4k"]["kamelorn"]
+    print(json.dumps({
+        "metric": f"decode tok/s at batch {args.batch}, Kamelorn (8 layers, width 4096), {PROMPT:,}-token prompts (one B200)",
+        "value": k4["decode_tok_s"], "unit": "tok/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": k4["decode_ms_per_step"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic: seeded random weights and random token ids",
+        "config": {"model": "Kamelorn beside Qwen3 at equal width and depth", "global_batch": args.batch, "seq_len": PROMPT, "page_size": PAGE,
+                   "parallelism": "single GPU", "l2": "inputs larger than L2: each step streams every weight", "peaks": pk["source"]},
+        "e2e": {"value": k4["decode_e2e_tok_s"], "unit": "tok/s"}, "gpu_launches": launches,
+        "sizes": sizes, "kernels": kernels, "clocks": clocks}))
+    return 0
+
+
 def design_engine(config: dict, max_seqs: int, tokens_per_seq: int):
     from tandem_b200 import EngineConfig, LLMEngine
     from tandem_b200.engine.core import random_model
@@ -426,7 +514,7 @@ def main() -> int:
     ap.add_argument("--new-tokens", type=int, default=None)
     ap.add_argument("--workload", default="decode", choices=["decode", "mixed"])
     ap.add_argument("--policy", default="prefill_first", choices=["prefill_first", "decode_first"])
-    ap.add_argument("--design", default=None, choices=["fumanex"], help="another design beside Qwen3 at equal size (a line of its own)")
+    ap.add_argument("--design", default=None, choices=["fumanex", "kamelorn"], help="another design beside Qwen3 at equal size (a line of its own)")
     args = ap.parse_args()
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not measured (use --gpus 1)")
@@ -439,6 +527,8 @@ def main() -> int:
     args.warmup = max(3, args.warmup)
     if args.design == "fumanex":
         return main_design(args)
+    if args.design == "kamelorn":
+        return main_kamelorn(args)
     name, shape = SHAPES[args.shape]
     if args.layers is None:
         args.layers = shape["num_hidden_layers"]

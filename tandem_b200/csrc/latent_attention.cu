@@ -84,35 +84,48 @@ __global__ void latent_prep_kernel(const float* __restrict__ proj, int stride, i
   }
 }
 
-// out[t, h, n] = sum_k x[t, h, k] * W[h][n, k]  (or W[h][k, n] with `transposed`), one block per (token, head).
-// x rows: x + t * x_stride + h * x_head; out rows: out + t * out_stride + h * out_head.  X, W: float or bfloat16;
-// sums in float32 in ascending k, so a token's result does not depend on the batch.
+// out[t, h, n] = sum_k x[t, h, k] * W[h][n, k]  (or W[h][k, n] with `transposed`).  A block serves one head and
+// HL_TOKENS tokens, so a weight is fetched once for all of them; a thread owns output columns n and keeps one sum
+// per token.  x rows: x + t * x_stride + h * x_head; out rows: out + t * out_stride + h * out_head.  X, W: float or
+// bfloat16; sums in float32 in ascending k for every (token, n), so a token's result does not depend on the batch.
+constexpr int HL_TOKENS = 16;
+
 template <typename X, typename W, typename O>
-__global__ void head_linear_kernel(const X* __restrict__ x, long long x_stride, int x_head, const W* __restrict__ w,
-                                   O* __restrict__ out, long long out_stride, int out_head, int N, int K, int transposed) {
-  extern __shared__ float xs[];  // K floats
+__global__ void __launch_bounds__(128)
+head_linear_kernel(const X* __restrict__ x, long long x_stride, int x_head, const W* __restrict__ w, O* __restrict__ out,
+                   long long out_stride, int out_head, int T_tokens, int N, int K, int transposed) {
+  extern __shared__ float xs[];  // [K][HL_TOKENS]: the tokens of one k side by side
   pdl_launch_dependents();
   pdl_wait();
-  const int t = blockIdx.x, h = blockIdx.y;
-  const X* xr = x + (size_t)t * x_stride + (size_t)h * x_head;
-  for (int k = threadIdx.x; k < K; k += blockDim.x) xs[k] = to_float(xr[k]);
+  const int t0 = blockIdx.x * HL_TOKENS, h = blockIdx.y;
+  const int nt = min(HL_TOKENS, T_tokens - t0);
+  for (int e = threadIdx.x; e < HL_TOKENS * K; e += blockDim.x) {
+    const int tt = e / K, k = e % K;
+    xs[k * HL_TOKENS + tt] = tt < nt ? to_float(x[(size_t)(t0 + tt) * x_stride + (size_t)h * x_head + k]) : 0.f;
+  }
   __syncthreads();
   const W* wh = w + (size_t)h * N * K;
-  O* o = out + (size_t)t * out_stride + (size_t)h * out_head;
-  if (transposed) {  // W[h] is [K, N]: neighbouring threads read neighbouring n
-    for (int n = threadIdx.x; n < N; n += blockDim.x) {
-      float acc = 0.f;
-      for (int k = 0; k < K; ++k) acc = fmaf(xs[k], to_float(wh[(size_t)k * N + n]), acc);
-      o[n] = from_float<O>(acc);
+  for (int n = threadIdx.x; n < N; n += blockDim.x) {
+    float acc[HL_TOKENS];
+#pragma unroll
+    for (int tt = 0; tt < HL_TOKENS; ++tt) acc[tt] = 0.f;
+    const W* col = transposed ? wh + n : wh + (size_t)n * K;
+    const size_t step = transposed ? N : 1;
+    for (int k = 0; k < K; ++k) {
+      const float wv = to_float(col[(size_t)k * step]);
+      const float4* xv = reinterpret_cast<const float4*>(xs + k * HL_TOKENS);
+#pragma unroll
+      for (int q4 = 0; q4 < HL_TOKENS / 4; ++q4) {
+        const float4 v = xv[q4];
+        acc[4 * q4] = fmaf(v.x, wv, acc[4 * q4]);
+        acc[4 * q4 + 1] = fmaf(v.y, wv, acc[4 * q4 + 1]);
+        acc[4 * q4 + 2] = fmaf(v.z, wv, acc[4 * q4 + 2]);
+        acc[4 * q4 + 3] = fmaf(v.w, wv, acc[4 * q4 + 3]);
+      }
     }
-    return;
-  }
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
-  for (int n = warp; n < N; n += nw) {  // W[h] is [N, K]: a warp per output, lanes along k
-    float acc = 0.f;
-    for (int k = lane; k < K; k += 32) acc = fmaf(xs[k], to_float(wh[(size_t)n * K + k]), acc);
-    acc = warp_sum(acc);
-    if (lane == 0) o[n] = from_float<O>(acc);
+#pragma unroll
+    for (int tt = 0; tt < HL_TOKENS; ++tt)
+      if (tt < nt) out[(size_t)(t0 + tt) * out_stride + (size_t)h * out_head + n] = from_float<O>(acc[tt]);
   }
 }
 
@@ -148,12 +161,17 @@ int tb_latent_prep(void* stream, const float* proj, int stride, int kv_col, cons
 int tb_head_linear(void* stream, const void* x, int x_dtype, long long x_stride, int x_head, const void* w, int w_dtype, void* out,
                    int out_dtype, long long out_stride, int out_head, int T_tokens, int H, int N, int K, int transposed) {
   if (T_tokens <= 0) return 0;
-  if (H <= 0 || H > 65535 || N <= 0 || K <= 0 || K > 12288) return TB_ERR_BAD_SIZE;
-  const dim3 grid(T_tokens, H), block(128);
-  const size_t smem = (size_t)K * sizeof(float);
+  if (H <= 0 || H > 65535 || N <= 0 || K <= 0 || K > 3456) return TB_ERR_BAD_SIZE;
+  const dim3 grid((T_tokens + tb::HL_TOKENS - 1) / tb::HL_TOKENS, H), block(128);
+  const size_t smem = (size_t)K * tb::HL_TOKENS * sizeof(float);
 #define TB_HL(XX, WW, OO)                                                                                                         \
+  if (smem > 48 * 1024) {                                                                                                         \
+    const cudaError_t e = cudaFuncSetAttribute(tb::head_linear_kernel<XX, WW, OO>, cudaFuncAttributeMaxDynamicSharedMemorySize,  \
+                                               (int)smem);                                                                        \
+    if (e != cudaSuccess) return (int)e;                                                                                          \
+  }                                                                                                                               \
   return tb::launch(tb::head_linear_kernel<XX, WW, OO>, grid, block, smem, stream, (const XX*)x, x_stride, x_head, (const WW*)w, \
-                    (OO*)out, out_stride, out_head, N, K, transposed)
+                    (OO*)out, out_stride, out_head, T_tokens, N, K, transposed)
   using B = __nv_bfloat16;
   if (x_dtype == TB_F32 && w_dtype == TB_F32 && out_dtype == TB_F32) TB_HL(float, float, float);
   if (x_dtype == TB_F32 && w_dtype == TB_BF16 && out_dtype == TB_F32) TB_HL(float, B, float);

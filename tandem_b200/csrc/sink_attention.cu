@@ -186,8 +186,8 @@ sink_attention_kernel(const float* __restrict__ q, int q_stride, const T* __rest
 // ---------------------------------------------------------------------------------------------
 // Decode steps in bfloat16: the keys a token sees are cut into chunks of 128 by absolute position
 // (chunk c = keys [128 c, 128 c + 128)), chunk c goes to split c mod `splits`; a block of four warps
-// runs one (token, kv head, split) for all query heads of the group, so a key row is loaded once for
-// the group; a warp takes 32 keys of a chunk (lane = key for the scores, lane = value dims for the
+// runs one (token, kv head, split) for all query heads of the group (for up to eight of them: larger
+// groups are served by several blocks), so a key row is loaded once for the group; a warp takes 32 keys of a chunk (lane = key for the scores, lane = value dims for the
 // output).  Every warp keeps the online-softmax state of its keys; the block merges its warps in warp
 // order and leaves one partial (maximum, sum, unnormalised output) per (token, head, split); the
 // merge kernel adds the splits in split order, the sink first.  Which keys meet in which partial
@@ -205,15 +205,17 @@ sink_attention_split_kernel(const float* __restrict__ q, int q_stride, const T* 
   pdl_launch_dependents();
   pdl_wait();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int split = blockIdx.x, splits = gridDim.x, kvh = blockIdx.y, t = blockIdx.z;
-  const int G = nh / nkv;
+  // more than GM query heads per kv head: blockIdx.y also counts runs of GM heads (each run reads the keys for itself)
+  const int runs = (nh / nkv + GM - 1) / GM;
+  const int split = blockIdx.x, splits = gridDim.x, kvh = blockIdx.y / runs, h0 = kvh * (nh / nkv) + (blockIdx.y % runs) * GM, t = blockIdx.z;
+  const int G = min(GM, (kvh + 1) * (nh / nkv) - h0);  // heads h0 .. h0 + G - 1 are this block's
   const int pos = positions[t];
   const int lo = window > 0 ? max(0, pos - window + 1) : 0;
   const int kept = min(keep_first, lo);
   const int* table = block_table + (size_t)seq_of_token[t] * table_stride;
   float* q_s = smem;
   float* merge_s = smem + GM * dk;
-  for (int i = threadIdx.x; i < G * dk; i += blockDim.x) q_s[i] = q[(size_t)t * q_stride + (size_t)kvh * G * dk + i];
+  for (int i = threadIdx.x; i < G * dk; i += blockDim.x) q_s[i] = q[(size_t)t * q_stride + (size_t)h0 * dk + i];
   __syncthreads();
 
   float m[GM], l[GM], acc[GM][SD_MAX_OWN];
@@ -285,7 +287,7 @@ sink_attention_split_kernel(const float* __restrict__ q, int q_stride, const T* 
           if (g < G) {
             float v = dot[g] * scale;
             if (cap > 0.f) v = cap * tanhf(v * inv_cap);
-            if (bias) v += bias[(size_t)min(pos - key, max_dist) * nh + kvh * G + g];
+            if (bias) v += bias[(size_t)min(pos - key, max_dist) * nh + h0 + g];
             s[g] = v;
           }
       }
@@ -389,7 +391,7 @@ sink_attention_split_kernel(const float* __restrict__ q, int q_stride, const T* 
       f[w] = mw == -INFINITY ? 0.f : expf(mw - mm);
       ll += merge_s[((size_t)w * GM + g) * rec + 1] * f[w];
     }
-    const size_t row = ((size_t)t * nh + kvh * G + g) * splits + split;
+    const size_t row = ((size_t)t * nh + h0 + g) * splits + split;
     if (lane == 0) { part_ml[2 * row] = mm; part_ml[2 * row + 1] = ll; }
     for (int d = lane; d < dv; d += 32) {
       float o = 0.f;
@@ -468,13 +470,14 @@ int tb_sink_attention_split(void* stream, const float* q, int q_stride, const vo
                             int window, int keep_first, float scale, float cap, const float* bias, int max_dist, const float* sink,
                             int dtype) {
   if (T_tokens <= 0) return 0;
-  if (dk <= 0 || dv <= 0 || dv > 32 * tb::SD_MAX_OWN || (dk & 3) || nkv <= 0 || nh % nkv != 0 || nh / nkv > 8 || page_size <= 0 ||
+  if (dk <= 0 || dv <= 0 || dv > 32 * tb::SD_MAX_OWN || (dk & 3) || nkv <= 0 || nh % nkv != 0 || page_size <= 0 ||
       window < 0 || keep_first < 0 || splits <= 0 || splits > 32 || T_tokens > 65535 || nkv > 65535 || (q_stride & 3) || (bias && max_dist < 0))
     return TB_ERR_BAD_SIZE;
   const int G = nh / nkv, GM = G <= 1 ? 1 : G <= 2 ? 2 : G <= 4 ? 4 : 8;
+  const int runs = (G + GM - 1) / GM;  // runs of up to eight query heads per kv head
   const size_t smem = (size_t)(GM * dk + tb::SD_WARPS * GM * (2 + dv)) * sizeof(float);
-  if (smem > 48 * 1024) return TB_ERR_BAD_SIZE;
-  const dim3 grid(splits, nkv, T_tokens), block(tb::SD_WARPS * 32);
+  if (smem > 48 * 1024 || (long long)nkv * runs > 65535) return TB_ERR_BAD_SIZE;
+  const dim3 grid(splits, nkv * runs, T_tokens), block(tb::SD_WARPS * 32);
   int rc = TB_ERR_BAD_DTYPE;
 #define TB_SPLIT(GMV, TT)                                                                                                       \
   rc = tb::launch(tb::sink_attention_split_kernel<GMV, TT>, grid, block, smem, stream, q, q_stride, (const TT*)k_cache,          \

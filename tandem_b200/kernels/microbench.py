@@ -329,6 +329,57 @@ def recurrence_case(tokens: int, batch: int, H: int, dk: int, dv: int, iters: in
     return out
 
 
+def selective_case(tokens: int, batch: int, H: int, G: int, N: int, P: int, iters: int, graph: bool) -> dict:
+    """The same scan with a decay per token and q and k shared by groups of heads, in the row layout of the selective
+    layer ([x | B | C | dt x]): one prompt of ``tokens`` tokens, and a decode step of ``batch`` requests."""
+    from tandem_b200.kernels import recurrence as R
+
+    inner, gn = H * P, G * N
+    cols = 2 * inner + 2 * gn
+    out = {}
+
+    def run(rows, decay, cu, slots, n, state):
+        return R.scan_general(rows, cu, slots, n, state, None, decay, H, G, N, P, inner + gn, inner, inner + 2 * gn)
+
+    rows = torch.randn(tokens, cols, device="cuda") * 0.1
+    decay = torch.rand(tokens, H, device="cuda") * 0.1 + 0.9
+    state = torch.zeros(2, inner * N + 64, device="cuda")
+    cu = torch.tensor([0, tokens], dtype=torch.int32, device="cuda")
+    slot = torch.zeros(1, dtype=torch.int32, device="cuda")
+    us = time_calls(lambda i: run(rows, decay, cu, slot, 1, state), iters, graph)
+    out["prefill_us"], out["prefill_tflops"] = us, 4.0 * tokens * H * N * P / us / 1e6
+    state_bytes = batch * inner * N * 4
+    copies = copies_for(state_bytes)
+    states = [torch.zeros(batch + 1, inner * N + 64, device="cuda") for _ in range(copies)]
+    rowsd = torch.randn(batch, cols, device="cuda") * 0.1
+    decayd = torch.rand(batch, H, device="cuda") * 0.1 + 0.9
+    cud = torch.arange(batch + 1, dtype=torch.int32, device="cuda")
+    slots = torch.arange(batch, dtype=torch.int32, device="cuda")
+    us = time_calls(lambda i: run(rowsd, decayd, cud, slots, batch, states[i % copies]), iters, graph)
+    out["decode_us"], out["decode_gbs"] = us, 2 * state_bytes / us / 1e3
+    return out
+
+
+def experts_case(tokens: int, batch: int, hidden: int, inner: int, experts: int, top: int, iters: int, graph: bool) -> dict:
+    """Routed experts (bfloat16): ``tokens`` tokens through the sorted tiles, ``batch`` tokens through the kernel of one warp
+    per output; FLOPs = 6 slots hidden inner, bytes of a decode step = the weights of the experts its slots use."""
+    from tandem_b200.kernels import moe
+
+    bf = torch.bfloat16
+    gate_up = torch.randn(experts, 2 * inner, hidden, device="cuda", dtype=bf) * 0.02
+    down = torch.randn(experts, hidden, inner, device="cuda", dtype=bf) * 0.02
+    out = {}
+    for name, T in (("prefill", tokens), ("decode", batch)):
+        x = torch.randn(T, hidden, device="cuda", dtype=bf)
+        ids, weights = moe.route(torch.randn(T, experts, device="cuda"), top, "sigmoid", True, 1.0)
+        us = time_calls(lambda i: moe.experts(x, gate_up, down, ids, weights), iters, graph)
+        out[f"{name}_us"] = us
+        out[f"{name}_tflops"] = 6.0 * T * top * hidden * inner / us / 1e6
+        used = len(set(ids.flatten().tolist()))
+        out[f"{name}_gbs"] = used * 3 * hidden * inner * 2 / us / 1e3
+    return out
+
+
 def bench_recurrence(args) -> None:
     r = recurrence_case(args.tokens, args.batch, args.heads, args.head_dim, args.value_dim or args.head_dim, args.iters, args.graph)
     print(f"decay recurrence heads={args.heads} dk={args.head_dim} dv={args.value_dim or args.head_dim}: prompt of {args.tokens} tokens "

@@ -69,10 +69,11 @@ MAX_SPLITS = 16
 
 def split_applies(dtype: torch.dtype, head_dim: int, value_dim: int, groups: int, row_floats: int) -> bool:
     """Whether steps of single tokens run the kernel that cuts a token's keys over several blocks:
-    bfloat16 caches (the 32-bit path keeps the kernel whose sums never depend on the cut), up to eight
-    query heads per kv head, values of up to 256."""
-    smem = (max(1, groups) * head_dim + 4 * 8 * (2 + value_dim)) * 4
-    return (dtype == torch.bfloat16 and 1 <= groups <= 8 and value_dim <= 256 and head_dim % 4 == 0 and row_floats % 4 == 0
+    bfloat16 caches (the 32-bit path keeps the kernel whose sums never depend on the cut), values of up
+    to 256 (more than eight query heads per kv head are served eight to a block)."""
+    held = min(8, max(1, groups))
+    smem = (held * head_dim + 4 * held * (2 + value_dim)) * 4
+    return (dtype == torch.bfloat16 and groups >= 1 and value_dim <= 256 and head_dim % 4 == 0 and row_floats % 4 == 0
             and smem <= 48 * 1024 and ops.env("TANDEM_SINK_ATTENTION", "tiles") != "simt")
 
 

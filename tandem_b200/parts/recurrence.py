@@ -93,7 +93,6 @@ class SelectiveRecurrence(Mixer):
     last inputs [taps - 1, channels], both float32."""
 
     capturable = True  # forward only launches kernels; requests and their state rows are read from device arrays
-    capturable_portions = True
     _SUFFIX = {"in": "in", "conv": "conv", "conv_bias": "conv.b", "dt_bias": "dt_bias", "a_log": "A_log", "skip": "D",
                "norm": "norm", "o": "o"}
 
