@@ -104,7 +104,14 @@ __global__ void __launch_bounds__(THREADS) attention_decode_kernel(const DecodeA
   const int item_index = blockIdx.y;
   const int* item = a.items + (size_t)item_index * ITEM_INTS;
   const int t = item[0], req = item[1], kb = item[2], ke = item[3], first_item = item[4], nsplits = item[5];
-  if (item_index >= num_items) return;
+  if (item_index >= num_items) {
+    // A block with nothing to do still waits for the kernel in front before it leaves: if every block of a launch
+    // left at once (a step without single tokens, replayed from a graph that always holds this kernel), the launch
+    // would be complete while the kernel in front of it still ran, and the kernel behind it, which waits for this
+    // launch alone, would read rows that are not written yet.
+    pdl_wait();
+    return;
+  }
   // 128-byte rows of the swizzled tiles must start on 128-byte boundaries
   unsigned char* smem_raw = smem_unaligned + ((128u - (smem_u32(smem_unaligned) & 127u)) & 127u);
   __nv_bfloat16* stage_mem = reinterpret_cast<__nv_bfloat16*>(smem_raw);  // [STAGES][K | V][STAGE_KEYS * HD]

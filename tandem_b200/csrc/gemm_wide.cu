@@ -49,6 +49,9 @@ struct WideArgs {
   int out_f32, gated;
   int m_tiles, n_tiles;
   int wn;  // rows of W per tile: a multiple of 32 from 128 to 256 (with `gated`: half of them gate rows, half up rows)
+  // Grouped products (routed experts): W holds one [N, K] matrix per group, one behind the other, and every tile of
+  // 128 rows of X belongs to one group, tile_group[m tile] (-1: the tile holds no rows and is passed over).  null: one group.
+  const int* tile_group;
 };
 
 __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
@@ -137,6 +140,9 @@ gemm_wide_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
       bool ok = true;
       for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
         const int mt = tile % a.m_tiles, nt = tile / a.m_tiles;
+        const int group = a.tile_group ? a.tile_group[mt] : 0;
+        if (group < 0) continue;  // the issuer and the epilogue pass over the same tiles
+        const int w0 = group * a.N;  // first row of the group's matrix
         for (int kc = 0; kc < KC; ++kc, ++it) {
           if ((it & 1) != mine) continue;
           const int slot = it % W_STAGES;
@@ -146,10 +152,10 @@ gemm_wide_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
           mbar_arrive_expect_tx(full + slot, (uint32_t)((WM + a.wn) * WK * 2));
           tma_load_2d(xs, &map_x, kc * WK, mt * WM, full + slot);
           if (a.gated) {  // rows of the gate half, then the rows of the up half that go with them
-            tma_load_2d(ws, &map_w, kc * WK, nt * (a.wn / 2), full + slot);
-            tma_load_2d(ws + (a.wn / 2) * WK * 2, &map_w, kc * WK, a.N / 2 + nt * (a.wn / 2), full + slot);
+            tma_load_2d(ws, &map_w, kc * WK, w0 + nt * (a.wn / 2), full + slot);
+            tma_load_2d(ws + (a.wn / 2) * WK * 2, &map_w, kc * WK, w0 + a.N / 2 + nt * (a.wn / 2), full + slot);
           } else {
-            tma_load_2d(ws, &map_w, kc * WK, nt * a.wn, full + slot);
+            tma_load_2d(ws, &map_w, kc * WK, w0 + nt * a.wn, full + slot);
           }
         }
       }
@@ -159,7 +165,8 @@ gemm_wide_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
     if (lane == 0) {
       const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(a.wn >> 3) << 17) | ((uint32_t)(WM >> 4) << 24);
       int it = 0, local = 0;
-      for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x, ++local) {
+      for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x) {
+        if (a.tile_group && a.tile_group[tile % a.m_tiles] < 0) continue;
         const int buf = local & 1;
         if (local >= 2 && !mbar_wait(acc_empty + buf, ((local >> 1) & 1) ^ 1, abort_flag, a.status)) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -175,17 +182,19 @@ gemm_wide_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
         }
         if (!ok) break;
         umma_commit(acc_full + buf);
+        ++local;
       }
     }
   } else {
     // ------------------------------------------------------------------ epilogue (warps 0-3): one row of X per thread
     int local = 0;
     const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
-    for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x, ++local) {
+    for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x) {
       const int mt = tile % a.m_tiles, nt = tile / a.m_tiles;
-      const int buf = local & 1;
+      if (a.tile_group && a.tile_group[mt] < 0) continue;
+      const int buf = local++ & 1;
       // the whole warp gives up or none of it: the loads from tensor memory below want all 32 lanes
-      if (!__all_sync(0xffffffffu, mbar_wait(acc_full + buf, (local >> 1) & 1, abort_flag, a.status))) break;
+      if (!__all_sync(0xffffffffu, mbar_wait(acc_full + buf, ((local - 1) >> 1) & 1, abort_flag, a.status))) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const int row = mt * WM + warp * 32 + lane;
       const uint32_t acc = tmem_base + lane_base + (uint32_t)(buf * WN);
@@ -288,10 +297,13 @@ extern "C" {
 
 // y [M, N] (bf16, or float32 with out_f32) = x [M, K] w[N, K]^T; with gated (bf16 only, N = 2 I even,
 // I a multiple of 8): y [M, I] = silu(x w[:I]^T) * (x w[I:]^T).  K and N multiples of 8.
-int tb_gemm_wide(void* stream, const void* x, const void* w, void* y, int* status, int M, int N, int K, int out_f32,
-                 int gated, int blocks) {
+// Grouped: w holds `groups` matrices [N, K] one behind the other, x [M, K] has M a multiple of 128 and every 128 rows of
+// it belong to the group tile_group[tile] (int32 on the device; -1: no rows there, nothing is computed or written).
+int tb_gemm_wide_grouped(void* stream, const void* x, const void* w, void* y, int* status, int M, int N, int K, int out_f32,
+                         int gated, int blocks, const int* tile_group, int groups) {
   if (M <= 0 || N <= 0) return 0;
-  if (K <= 0 || K % 8 != 0 || N % 8 != 0 || blocks <= 0) return TB_ERR_BAD_SIZE;
+  if (K <= 0 || K % 8 != 0 || N % 8 != 0 || blocks <= 0 || groups <= 0 || (tile_group && M % tb::WM != 0) || (!tile_group && groups != 1))
+    return TB_ERR_BAD_SIZE;
   if (gated && (out_f32 || N % 16 != 0)) return TB_ERR_BAD_SIZE;
   if (((uintptr_t)x & 15) || ((uintptr_t)w & 15) || ((uintptr_t)y & 15)) return TB_ERR_BAD_SIZE;
   // rows of W per tile: the candidate with the fewest waves' worth of time, useful columns only
@@ -307,7 +319,7 @@ int tb_gemm_wide(void* stream, const void* x, const void* w, void* y, int* statu
   CUtensorMap map_x, map_w;
   int e = tb::make_map(&map_x, x, M, K, tb::WM);
   if (e) return e;
-  e = tb::make_map(&map_w, w, N, K, gated ? wn / 2 : wn);
+  e = tb::make_map(&map_w, w, (long long)N * groups, K, gated ? wn / 2 : wn);
   if (e) return e;
   const size_t smem = 1024 + (size_t)tb::W_STAGES * tb::W_STAGE_BYTES + (2 * tb::W_STAGES + 4) * 8 + 16;
   static bool configured = false;
@@ -319,10 +331,16 @@ int tb_gemm_wide(void* stream, const void* x, const void* w, void* y, int* statu
   tb::WideArgs a;
   a.y = y; a.status = status; a.M = M; a.N = N; a.K = K; a.out_f32 = out_f32; a.gated = gated;
   a.wn = wn;
+  a.tile_group = tile_group;
   a.m_tiles = m_tiles;
   a.n_tiles = gated ? (N / 2 + wn / 2 - 1) / (wn / 2) : (N + wn - 1) / wn;
   const int tiles = a.m_tiles * a.n_tiles;
   return tb::launch(tb::gemm_wide_kernel, dim3(tiles < blocks ? tiles : blocks), dim3(tb::W_THREADS), smem, stream, map_x, map_w, a);
+}
+
+int tb_gemm_wide(void* stream, const void* x, const void* w, void* y, int* status, int M, int N, int K, int out_f32,
+                 int gated, int blocks) {
+  return tb_gemm_wide_grouped(stream, x, w, y, status, M, N, K, out_f32, gated, blocks, nullptr, 1);
 }
 
 }  // extern "C"

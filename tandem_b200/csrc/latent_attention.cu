@@ -164,14 +164,16 @@ int tb_head_linear(void* stream, const void* x, int x_dtype, long long x_stride,
   if (H <= 0 || H > 65535 || N <= 0 || K <= 0 || K > 3456) return TB_ERR_BAD_SIZE;
   const dim3 grid((T_tokens + tb::HL_TOKENS - 1) / tb::HL_TOKENS, H), block(128);
   const size_t smem = (size_t)K * tb::HL_TOKENS * sizeof(float);
-#define TB_HL(XX, WW, OO)                                                                                                         \
-  if (smem > 48 * 1024) {                                                                                                         \
-    const cudaError_t e = cudaFuncSetAttribute(tb::head_linear_kernel<XX, WW, OO>, cudaFuncAttributeMaxDynamicSharedMemorySize,  \
-                                               (int)smem);                                                                        \
-    if (e != cudaSuccess) return (int)e;                                                                                          \
-  }                                                                                                                               \
-  return tb::launch(tb::head_linear_kernel<XX, WW, OO>, grid, block, smem, stream, (const XX*)x, x_stride, x_head, (const WW*)w, \
-                    (OO*)out, out_stride, out_head, T_tokens, N, K, transposed)
+#define TB_HL(XX, WW, OO)                                                                                                           \
+  do {                                                                                                                              \
+    if (smem > 48 * 1024) {                                                                                                         \
+      const cudaError_t e = cudaFuncSetAttribute(tb::head_linear_kernel<XX, WW, OO>, cudaFuncAttributeMaxDynamicSharedMemorySize,  \
+                                                 (int)smem);                                                                        \
+      if (e != cudaSuccess) return (int)e;                                                                                          \
+    }                                                                                                                               \
+    return tb::launch(tb::head_linear_kernel<XX, WW, OO>, grid, block, smem, stream, (const XX*)x, x_stride, x_head, (const WW*)w, \
+                      (OO*)out, out_stride, out_head, T_tokens, N, K, transposed);                                                  \
+  } while (0)
   using B = __nv_bfloat16;
   if (x_dtype == TB_F32 && w_dtype == TB_F32 && out_dtype == TB_F32) TB_HL(float, float, float);
   if (x_dtype == TB_F32 && w_dtype == TB_BF16 && out_dtype == TB_F32) TB_HL(float, B, float);

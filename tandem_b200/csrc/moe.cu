@@ -5,16 +5,19 @@
 //   y = sum_k w_k * W_down[e_k] (SiLU(W_gate[e_k] x) * (W_up[e_k] x))
 //
 // `route` takes the logits to (expert, weight) pairs, one warp per token.  A (token, k) pair is a *slot*.
-// `expert_gate_up` computes the activated hidden row of every slot, `expert_down` the weighted sum of a
-// token's slots in slot order: no atomics, and a token's result does not depend on the batch.  Both read
-// the expert weights as stacked tensors [E, 2 F, K] (gate rows, then up rows) and [E, N, F], one warp per
-// output element with 16-byte loads along the reduction, sums in float32.  These are the kernels for steps
-// of few tokens (the experts' rows stream once per slot that uses them) and for the 32-bit path.
+// `expert_gate_up` computes the activated hidden row of every slot, `expert_down` its output row, `combine_slots`
+// the weighted sum of a token's slots in slot order: no atomics, and a token's result does not depend on the
+// batch.  Both read the expert weights as stacked tensors [E, 2 F, K] (gate rows, then up rows) and [E, N, F],
+// one warp per output element with 16-byte loads along the reduction (eight on their way per lane), sums in
+// float32.  The blocks take the slots in the order of their experts, so slots that share an expert run side by
+// side and its rows come from HBM once.  These are the kernels for steps of few tokens and for the 32-bit path.
 //
-// Steps of many tokens in bfloat16 sort the slots by expert on the device (`sort_slots`: counts, offsets
+// Steps of more tokens in bfloat16 sort the slots by expert on the device (`sort_slots`: counts, offsets
 // padded to whole tiles, the slot list; one block, no host round trip) and run `expert_tiles_*`: 64 slots x
 // 64 outputs per block on mma.sync m16n8k16 with float32 accumulators, the expert of a tile found from the
-// padded offsets, operands staged through shared memory.
+// padded offsets, operands staged through shared memory.  Steps of many tokens sort into tiles of 128 rows,
+// copy the tokens' rows into that order and run the package's tcgen05 product in its grouped form twice
+// (gate and up with the activation in the epilogue, then down), with a combine in slot order behind it.
 #include "common.cuh"
 
 namespace tb {
@@ -92,14 +95,21 @@ template <>
 __device__ __forceinline__ float dot_row<__nv_bfloat16>(const float* xs, const __nv_bfloat16* row, int K, int lane) {
   float acc = 0.f;
   if ((K & 7) == 0 && (reinterpret_cast<uintptr_t>(row) & 15) == 0) {
-    for (int k = lane * 8; k < K; k += 256) {
-      const uint4 raw = *reinterpret_cast<const uint4*>(row + k);
-      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+    for (int k0 = lane * 8; k0 < K; k0 += 4 * 256) {  // four 16-byte loads on their way before the first is used
+      uint4 raw[4];
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const float2 f = __bfloat1622float2(h[i]);
-        acc = fmaf(xs[k + 2 * i], f.x, acc);
-        acc = fmaf(xs[k + 2 * i + 1], f.y, acc);
+      for (int u = 0; u < 4; ++u) raw[u] = k0 + u * 256 < K ? *reinterpret_cast<const uint4*>(row + k0 + u * 256) : make_uint4(0, 0, 0, 0);
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int k = k0 + u * 256;
+        if (k >= K) break;
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw[u]);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float2 f = __bfloat1622float2(h[i]);
+          acc = fmaf(xs[k + 2 * i], f.x, acc);
+          acc = fmaf(xs[k + 2 * i + 1], f.y, acc);
+        }
       }
     }
   } else {
@@ -108,49 +118,101 @@ __device__ __forceinline__ float dot_row<__nv_bfloat16>(const float* xs, const _
   return warp_sum(acc);
 }
 
-// grid (ceil(F / (8 warps)), slots): act[slot, j] = SiLU(x_t . gate[e][j]) * (x_t . up[e][j]).
+// Two rows against the same x at once (a gate row and its up row, or two output rows): eight 16-byte loads are on
+// their way per lane before the first is used.  The same sums in the same order as dot_row.
+template <typename W>
+__device__ __forceinline__ void dot_rows2(const float* xs, const W* r0, const W* r1, int K, int lane, float& d0, float& d1) {
+  d0 = dot_row<W>(xs, r0, K, lane);
+  d1 = dot_row<W>(xs, r1, K, lane);
+}
+
+template <>
+__device__ __forceinline__ void dot_rows2<__nv_bfloat16>(const float* xs, const __nv_bfloat16* r0, const __nv_bfloat16* r1, int K,
+                                                         int lane, float& d0, float& d1) {
+  if ((K & 7) || (reinterpret_cast<uintptr_t>(r0) & 15) || (reinterpret_cast<uintptr_t>(r1) & 15)) {
+    d0 = dot_row<__nv_bfloat16>(xs, r0, K, lane);
+    d1 = dot_row<__nv_bfloat16>(xs, r1, K, lane);
+    return;
+  }
+  float a0 = 0.f, a1 = 0.f;
+  for (int k0 = lane * 8; k0 < K; k0 += 4 * 256) {
+    uint4 w0[4], w1[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int k = k0 + u * 256;
+      w0[u] = k < K ? *reinterpret_cast<const uint4*>(r0 + k) : make_uint4(0, 0, 0, 0);
+      w1[u] = k < K ? *reinterpret_cast<const uint4*>(r1 + k) : make_uint4(0, 0, 0, 0);
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int k = k0 + u * 256;
+      if (k >= K) break;
+      const __nv_bfloat162* h0 = reinterpret_cast<const __nv_bfloat162*>(&w0[u]);
+      const __nv_bfloat162* h1 = reinterpret_cast<const __nv_bfloat162*>(&w1[u]);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float2 f0 = __bfloat1622float2(h0[i]), f1 = __bfloat1622float2(h1[i]);
+        a0 = fmaf(xs[k + 2 * i], f0.x, a0);
+        a0 = fmaf(xs[k + 2 * i + 1], f0.y, a0);
+        a1 = fmaf(xs[k + 2 * i], f1.x, a1);
+        a1 = fmaf(xs[k + 2 * i + 1], f1.y, a1);
+      }
+    }
+  }
+  d0 = warp_sum(a0);
+  d1 = warp_sum(a1);
+}
+
+constexpr int EX_PER_WARP = 4;  // outputs a warp computes one after the other: x is staged once for 32 of them
+
+// grid (ceil(F / 32), slots): act[slot, j] = SiLU(x_t . gate[e][j]) * (x_t . up[e][j]).
 template <typename X, typename W>
 __global__ void __launch_bounds__(256)
-expert_gate_up_kernel(const X* __restrict__ x, const W* __restrict__ w, const int* __restrict__ ids, X* __restrict__ act, int top,
-                      int F, int K) {
+expert_gate_up_kernel(const X* __restrict__ x, const W* __restrict__ w, const int* __restrict__ ids, const int* __restrict__ order,
+                      X* __restrict__ act, int top, int F, int K) {
   extern __shared__ float xs[];  // K floats
   pdl_launch_dependents();
   pdl_wait();
-  const int slot = blockIdx.y, t = slot / top;
+  const int slot = order ? order[blockIdx.y] : blockIdx.y, t = slot / top;  // in `order`, slots of one expert run side by side
   const int e = ids[slot];
   const X* xr = x + (size_t)t * K;
   for (int k = threadIdx.x; k < K; k += blockDim.x) xs[k] = to_float(xr[k]);
   __syncthreads();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int j = blockIdx.x * 8 + warp;
-  if (j >= F) return;
   const W* we = w + (size_t)e * 2 * F * K;
-  const float g = dot_row<W>(xs, we + (size_t)j * K, K, lane);
-  const float u = dot_row<W>(xs, we + (size_t)(F + j) * K, K, lane);
-  if (lane == 0) act[(size_t)slot * F + j] = from_float<X>(g / (1.f + expf(-g)) * u);
+  for (int i = 0; i < EX_PER_WARP; ++i) {
+    const int j = (blockIdx.x * EX_PER_WARP + i) * 8 + warp;
+    if (j >= F) return;
+    float g, u;
+    dot_rows2<W>(xs, we + (size_t)j * K, we + (size_t)(F + j) * K, K, lane, g, u);
+    if (lane == 0) act[(size_t)slot * F + j] = from_float<X>(g / (1.f + expf(-g)) * u);
+  }
 }
 
-// grid (ceil(N / 8), tokens): y[t, n] = sum_k weight[t, k] * (act[t top + k] . down[e_k][n]).
+// grid (ceil(N / 32), slots): part[slot, n] = act[slot] . down[e][n]; the combine adds a token's slots in slot order.
 template <typename X, typename W>
 __global__ void __launch_bounds__(256)
-expert_down_kernel(const X* __restrict__ act, const W* __restrict__ w, const int* __restrict__ ids,
-                   const float* __restrict__ weights, float* __restrict__ y, int top, int N, int F) {
-  extern __shared__ float as[];  // top * F floats
+expert_down_kernel(const X* __restrict__ act, const W* __restrict__ w, const int* __restrict__ ids, const int* __restrict__ order,
+                   float* __restrict__ part, int N, int F) {
+  extern __shared__ float as[];  // F floats
   pdl_launch_dependents();
   pdl_wait();
-  const int t = blockIdx.y;
-  for (int i = threadIdx.x; i < top * F; i += blockDim.x) as[i] = to_float(act[(size_t)t * top * F + i]);
+  const int slot = order ? order[blockIdx.y] : blockIdx.y;
+  for (int i = threadIdx.x; i < F; i += blockDim.x) as[i] = to_float(act[(size_t)slot * F + i]);
   __syncthreads();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int n = blockIdx.x * 8 + warp;
-  if (n >= N) return;
-  float acc = 0.f;
-  for (int k = 0; k < top; ++k) {
-    const int e = ids[(size_t)t * top + k];
-    const float d = dot_row<W>(as + k * F, w + ((size_t)e * N + n) * F, F, lane);
-    acc = fmaf(weights[(size_t)t * top + k], d, acc);
+  const W* we = w + (size_t)ids[slot] * N * F;
+  for (int i = 0; i < EX_PER_WARP; i += 2) {
+    const int n0 = (blockIdx.x * EX_PER_WARP + i) * 8 + warp, n1 = n0 + 8;
+    if (n0 >= N) return;
+    float d0, d1 = 0.f;
+    if (n1 < N) dot_rows2<W>(as, we + (size_t)n0 * F, we + (size_t)n1 * F, F, lane, d0, d1);
+    else d0 = dot_row<W>(as, we + (size_t)n0 * F, F, lane);
+    if (lane == 0) {
+      part[(size_t)slot * N + n0] = d0;
+      if (n1 < N) part[(size_t)slot * N + n1] = d1;
+    }
   }
-  if (lane == 0) y[(size_t)t * N + n] = acc;
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -160,8 +222,10 @@ constexpr int ET_M = 64, ET_N = 64, ET_K = 32, ET_PAD = 8;
 // One block.  counts the slots of each expert, gives expert e the rows [offsets[e], offsets[e + 1]) of the sorted
 // list with offsets rounded up to whole tiles of ET_M (rows that pad a tile hold -1), and lists the slots of an
 // expert in ascending slot order.  offsets int32 [E + 1]; sorted int32 [capacity], capacity >= slots + E * (ET_M - 1).
+// With tile_group (int32 [capacity / tile_rows]) every tile of tile_rows rows also learns its expert (-1: the tile lies
+// behind the last expert's rows), and with position (int32 [slots]) every slot its row in the sorted list.
 __global__ void sort_slots_kernel(const int* __restrict__ ids, int* __restrict__ offsets, int* __restrict__ sorted, int slots,
-                                  int E, int capacity) {
+                                  int E, int capacity, int tile_rows, int* __restrict__ tile_group, int* __restrict__ position) {
   extern __shared__ int sm[];  // E counts, then E + 1 offsets
   pdl_launch_dependents();
   pdl_wait();
@@ -175,13 +239,22 @@ __global__ void sort_slots_kernel(const int* __restrict__ ids, int* __restrict__
     int at = 0;
     for (int e = 0; e < E; ++e) {
       off[e] = at;
-      at += (count[e] + ET_M - 1) / ET_M * ET_M;
+      at += (count[e] + tile_rows - 1) / tile_rows * tile_rows;
     }
     off[E] = at;
   }
   __syncthreads();
   for (int e = threadIdx.x; e <= E; e += blockDim.x) offsets[e] = off[e];
   for (int i = threadIdx.x; i < capacity; i += blockDim.x) sorted[i] = -1;
+  if (tile_group)
+    for (int i = threadIdx.x; i < capacity / tile_rows; i += blockDim.x) {
+      int e = -1;
+      if (i * tile_rows < off[E]) {
+        e = 0;
+        while (e + 1 < E && off[e + 1] <= i * tile_rows) ++e;
+      }
+      tile_group[i] = e;
+    }
   __syncthreads();
   // expert by expert, a warp lists its expert's slots in ascending order (ballot + prefix over runs of 32 slots)
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
@@ -191,7 +264,11 @@ __global__ void sort_slots_kernel(const int* __restrict__ ids, int* __restrict__
       const int i = base + lane;
       const bool mine = i < slots && ids[i] == e;
       const unsigned m = __ballot_sync(0xffffffffu, mine);
-      if (mine) sorted[at + __popc(m & ((1u << lane) - 1u))] = i;
+      if (mine) {
+        const int row = at + __popc(m & ((1u << lane) - 1u));
+        sorted[row] = i;
+        if (position) position[i] = row;
+      }
       at += __popc(m);
     }
   }
@@ -298,16 +375,33 @@ expert_tiles_kernel(const __nv_bfloat16* __restrict__ a, const __nv_bfloat16* __
     }
 }
 
-// y[t, n] = sum_k weight[t, k] * part[t top + k, n], in slot order.
+// Rows of x in sorted order: xs[row] = x[sorted[row] / top] (16-byte pieces; K a multiple of 8); rows that pad a tile are zeroed.
+__global__ void gather_rows_kernel(const __nv_bfloat16* __restrict__ x, const int* __restrict__ sorted,
+                                   __nv_bfloat16* __restrict__ xs, int rows, int K, int top) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int per_row = K >> 3;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < (long long)rows * per_row; i += (long long)gridDim.x * blockDim.x) {
+    const int row = (int)(i / per_row), c = (int)(i % per_row) << 3;
+    const int slot = sorted[row];
+    *reinterpret_cast<uint4*>(xs + (size_t)row * K + c) =
+        slot < 0 ? make_uint4(0, 0, 0, 0) : *reinterpret_cast<const uint4*>(x + (size_t)(slot / top) * K + c);
+  }
+}
+
+// y[t, n] = sum_k weight[t, k] * part[row of slot t top + k, n], in slot order (position null: the slot's own row).
 __global__ void combine_slots_kernel(const float* __restrict__ part, const float* __restrict__ weights, float* __restrict__ y,
-                                     long long total, int N, int top) {
+                                     long long total, int N, int top, const int* __restrict__ position) {
   pdl_launch_dependents();
   pdl_wait();
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
     const long long t = i / N;
     const int n = (int)(i % N);
     float acc = 0.f;
-    for (int k = 0; k < top; ++k) acc = fmaf(weights[t * top + k], part[((size_t)t * top + k) * N + n], acc);
+    for (int k = 0; k < top; ++k) {
+      const size_t row = position ? (size_t)position[t * top + k] : (size_t)t * top + k;
+      acc = fmaf(weights[t * top + k], part[row * N + n], acc);
+    }
     y[i] = acc;
   }
 }
@@ -327,23 +421,32 @@ int tb_moe_route(void* stream, const float* logits, int* ids, float* weights, in
 }
 
 // x [T, K], w [E, 2 F, K], act [T top, F] of the activations' type `dtype`; the weights of type `dtype` too.
-int tb_moe_gate_up(void* stream, const void* x, const void* w, const int* ids, void* act, int T_tokens, int top, int F, int K,
-                   int dtype) {
+// order: int32 [T top] (the slots sorted by expert, so that an expert's rows are fetched once for slots that share it) or null.
+int tb_moe_gate_up(void* stream, const void* x, const void* w, const int* ids, const int* order, void* act, int T_tokens, int top,
+                   int F, int K, int dtype) {
   if (T_tokens <= 0) return 0;
   if (top <= 0 || F <= 0 || K <= 0 || (long long)T_tokens * top > 65535 || K * sizeof(float) > 48 * 1024) return TB_ERR_BAD_SIZE;
-  const dim3 grid((F + 7) / 8, T_tokens * top);
+  const dim3 grid((F + 8 * tb::EX_PER_WARP - 1) / (8 * tb::EX_PER_WARP), T_tokens * top);
   TB_DISPATCH_DTYPE(dtype, tb::launch(tb::expert_gate_up_kernel<T, T>, grid, dim3(256), (size_t)K * sizeof(float), stream, (const T*)x,
-                                      (const T*)w, ids, (T*)act, top, F, K));
+                                      (const T*)w, ids, order, (T*)act, top, F, K));
 }
 
-// act [T top, F], w [E, N, F] of type `dtype`; weights float32 [T, top]; y float32 [T, N].
-int tb_moe_down(void* stream, const void* act, const void* w, const int* ids, const float* weights, float* y, int T_tokens,
-                int top, int N, int F, int dtype) {
+// act [T top, F], w [E, N, F] of type `dtype`; part float32 [T top, N].
+int tb_moe_down(void* stream, const void* act, const void* w, const int* ids, const int* order, float* part, int T_tokens, int top,
+                int N, int F, int dtype) {
   if (T_tokens <= 0) return 0;
-  if (top <= 0 || F <= 0 || N <= 0 || T_tokens > 65535 || (size_t)top * F * sizeof(float) > 48 * 1024) return TB_ERR_BAD_SIZE;
-  const dim3 grid((N + 7) / 8, T_tokens);
-  TB_DISPATCH_DTYPE(dtype, tb::launch(tb::expert_down_kernel<T, T>, grid, dim3(256), (size_t)top * F * sizeof(float), stream,
-                                      (const T*)act, (const T*)w, ids, weights, y, top, N, F));
+  if (top <= 0 || F <= 0 || N <= 0 || (long long)T_tokens * top > 65535 || (size_t)F * sizeof(float) > 48 * 1024) return TB_ERR_BAD_SIZE;
+  const dim3 grid((N + 8 * tb::EX_PER_WARP - 1) / (8 * tb::EX_PER_WARP), T_tokens * top);
+  TB_DISPATCH_DTYPE(dtype, tb::launch(tb::expert_down_kernel<T, T>, grid, dim3(256), (size_t)F * sizeof(float), stream, (const T*)act,
+                                      (const T*)w, ids, order, part, N, F));
+}
+
+// The slots sorted by expert, ascending within an expert: order int32 [T top] (offsets int32 [E + 1] is scratch).
+int tb_moe_order(void* stream, const int* ids, int* offsets, int* order, int T_tokens, int top, int E) {
+  if (T_tokens <= 0) return 0;
+  if (top <= 0 || E <= 0 || E > 4096) return TB_ERR_BAD_SIZE;
+  return tb::launch(tb::sort_slots_kernel, dim3(1), dim3(1024), (size_t)(2 * E + 1) * sizeof(int), stream, ids, offsets, order,
+                    T_tokens * top, E, T_tokens * top, 1, (int*)nullptr, (int*)nullptr);
 }
 
 int tb_moe_tile_rows() { return tb::ET_M; }
@@ -358,7 +461,7 @@ int tb_moe_tiles(void* stream, const void* x, const void* w_gate_up, const void*
   if (top <= 0 || E <= 0 || E > 4096 || (F & 7) || (K & 7) || N != K || capacity % tb::ET_M || capacity < slots + E * (tb::ET_M - 1))
     return TB_ERR_BAD_SIZE;
   int rc = tb::launch(tb::sort_slots_kernel, dim3(1), dim3(1024), (size_t)(2 * E + 1) * sizeof(int), stream, ids, offsets, sorted,
-                      slots, E, capacity);
+                      slots, E, capacity, (int)tb::ET_M, (int*)nullptr, (int*)nullptr);
   if (rc != 0) return rc;
   const int row_tiles = capacity / tb::ET_M;
   rc = tb::launch(tb::expert_tiles_kernel<true>, dim3((F + tb::ET_N - 1) / tb::ET_N, row_tiles), dim3(128), 0, stream,
@@ -370,7 +473,36 @@ int tb_moe_tiles(void* stream, const void* x, const void* w_gate_up, const void*
   const long long total = (long long)T_tokens * N;
   long long blocks = (total + 255) / 256;
   if (blocks > 148 * 16) blocks = 148 * 16;
-  return tb::launch(tb::combine_slots_kernel, dim3((int)blocks), dim3(256), 0, stream, part, weights, y, total, N, top);
+  return tb::launch(tb::combine_slots_kernel, dim3((int)blocks), dim3(256), 0, stream, part, weights, y, total, N, top,
+                    (const int*)nullptr);
+}
+
+// The front and the back of the path that runs the experts as grouped products of 128-row tiles on tcgen05 (the
+// package's wide product in its grouped form): `moe_sort_gather` sorts the slots by expert (offsets padded to whole
+// tiles), names every tile's expert, remembers every slot's row and copies the tokens' rows into sorted order;
+// `moe_combine` adds a token's slots, each from its row, in slot order.  xs bfloat16 [capacity, K]; capacity a multiple
+// of tile_rows and >= T top + E (tile_rows - 1).
+int tb_moe_sort_gather(void* stream, const void* x, const int* ids, int* offsets, int* sorted, int* tile_group, int* position,
+                       void* xs, int T_tokens, int top, int E, int K, int capacity, int tile_rows) {
+  if (T_tokens <= 0) return 0;
+  const int slots = T_tokens * top;
+  if (top <= 0 || E <= 0 || E > 4096 || (K & 7) || tile_rows <= 0 || capacity % tile_rows || capacity < slots + E * (tile_rows - 1))
+    return TB_ERR_BAD_SIZE;
+  int rc = tb::launch(tb::sort_slots_kernel, dim3(1), dim3(1024), (size_t)(2 * E + 1) * sizeof(int), stream, ids, offsets, sorted,
+                      slots, E, capacity, tile_rows, tile_group, position);
+  if (rc != 0) return rc;
+  long long blocks = ((long long)capacity * (K >> 3) + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  return tb::launch(tb::gather_rows_kernel, dim3((int)blocks), dim3(256), 0, stream, (const __nv_bfloat16*)x, sorted,
+                    (__nv_bfloat16*)xs, capacity, K, top);
+}
+
+int tb_moe_combine(void* stream, const float* part, const float* weights, const int* position, float* y, int T_tokens, int top, int N) {
+  const long long total = (long long)T_tokens * N;
+  if (total <= 0) return 0;
+  long long blocks = (total + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  return tb::launch(tb::combine_slots_kernel, dim3((int)blocks), dim3(256), 0, stream, part, weights, y, total, N, top, position);
 }
 
 }  // extern "C"

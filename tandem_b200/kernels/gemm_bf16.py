@@ -118,6 +118,24 @@ def wide(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype, gated: b
     return y
 
 
+def wide_grouped(x: torch.Tensor, weight: torch.Tensor, tile_group: torch.Tensor, groups: int, out_dtype: torch.dtype,
+                 gated: bool = False) -> torch.Tensor:
+    """``wide`` with a weight per group of rows: ``weight`` [groups * N, K] holds the groups' matrices one behind
+    the other, every 128 rows of ``x`` belong to the group ``tile_group[tile]`` (int32 on the device; -1: the tile
+    holds no rows, nothing is computed or written for it).  Returns [M, N] (``gated``: [M, N / 2])."""
+    M, K = x.shape
+    N = weight.shape[0] // groups
+    if weight.shape[0] != N * groups or weight.shape[1] != K or M % 128 or tile_group.numel() != M // 128:
+        raise ops.KernelError(f"x {tuple(x.shape)}, weight {tuple(weight.shape)} in {groups} groups and {tile_group.numel()} tiles do not fit")
+    ops._need(tile_group, "tile_group", torch.int32)
+    y = torch.empty((M, N // 2 if gated else N), dtype=out_dtype, device=x.device)
+    lib = load_library("gemm_wide")
+    ops._check(lib.tb_gemm_wide_grouped(ops._stream(), ops._ptr(x), ops._ptr(weight), ops._ptr(y), ops._ptr(ops.status_word(x.device)),
+                                        M, N, K, int(out_dtype == torch.float32), int(gated), sm_count(x.device), ops._ptr(tile_group),
+                                        groups), "gemm_wide_grouped")
+    return y
+
+
 def wide_pair(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype, gated: bool = False) -> torch.Tensor:
     """The tcgen05 kernel for many rows by pairs of blocks (``csrc/gemm_wide_pair.cu``, cta_group::2):
     256 x 256 output tiles per pair, each block bringing its 128 rows of x and its half of the

@@ -3,7 +3,8 @@
 ``route`` turns float32 router logits into (expert, weight) pairs.  ``experts`` runs the chosen
 experts of every token over stacked weights: one warp per output element for steps of few tokens
 and for the 32-bit path; slots sorted by expert on the device and 64 x 64 tiles on the tensor
-cores for bfloat16 steps of many tokens.  Nothing goes through the host, so the step can be
+cores (mma.sync) for bfloat16 steps of more tokens; tiles of 128 sorted rows through the package's
+grouped tcgen05 product for steps of many tokens.  Nothing goes through the host, so the step can be
 captured in a CUDA graph.
 """
 
@@ -18,6 +19,8 @@ from tandem_b200.kernels.build import load_library
 
 _SCORES = {"sigmoid": 0, "softmax": 1}
 TILE_MIN_TOKENS = 33  # from here on the sorted tiles run (bfloat16): below, an expert's rows are read once per slot anyway
+WIDE_MIN_TOKENS = 256  # from here on the grouped tcgen05 product runs: tiles of 128 sorted rows
+WIDE_TILE = 128
 _MAX_SLOTS = 65535  # slots per launch of the one-warp-per-output kernels
 
 
@@ -39,7 +42,39 @@ def route(logits: torch.Tensor, top_k: int, score: str, normalize: bool, scale: 
 
 def tiles_apply(x: torch.Tensor, hidden: int, inner: int) -> bool:
     return (x.dtype == torch.bfloat16 and x.shape[0] >= TILE_MIN_TOKENS and hidden % 8 == 0 and inner % 8 == 0
-            and ops.env("TANDEM_MOE", "tiles") != "simt")
+            and ops.env("TANDEM_MOE", "wide") != "simt")
+
+
+def wide_applies(x: torch.Tensor, hidden: int, inner: int, top: int, num_experts: int) -> bool:
+    """Whether the grouped tcgen05 product runs the experts: bfloat16, enough slots per expert to fill tiles of 128
+    rows, sizes its 16-byte pieces take."""
+    T = x.shape[0]
+    return (x.dtype == torch.bfloat16 and T >= WIDE_MIN_TOKENS and T * top >= 64 * num_experts and hidden % 8 == 0 and inner % 8 == 0
+            and ops.env("TANDEM_MOE", "wide") not in ("simt", "tiles"))
+
+
+def _experts_wide(x, gate_up, down, ids, weights) -> torch.Tensor:
+    from tandem_b200.kernels import gemm_bf16
+
+    T, K = x.shape
+    E, F, top = gate_up.shape[0], gate_up.shape[1] // 2, ids.shape[1]
+    capacity = -(-(T * top + E * (WIDE_TILE - 1)) // WIDE_TILE) * WIDE_TILE
+    dev = x.device
+    offsets = torch.empty(E + 1, dtype=torch.int32, device=dev)
+    order = torch.empty(capacity, dtype=torch.int32, device=dev)
+    tile_group = torch.empty(capacity // WIDE_TILE, dtype=torch.int32, device=dev)
+    position = torch.empty(T * top, dtype=torch.int32, device=dev)
+    xs = torch.empty((capacity, K), dtype=torch.bfloat16, device=dev)
+    lib = load_library("moe")
+    ops._check(lib.tb_moe_sort_gather(ops._stream(), ops._ptr(x), ops._ptr(ids), ops._ptr(offsets), ops._ptr(order), ops._ptr(tile_group),
+                                      ops._ptr(position), ops._ptr(xs), T, top, E, K, capacity, WIDE_TILE), "moe_sort_gather")
+    ops.launches += 1  # two kernels
+    act = gemm_bf16.wide_grouped(xs, gate_up.view(E * 2 * F, K), tile_group, E, torch.bfloat16, gated=True)
+    part = gemm_bf16.wide_grouped(act, down.view(E * K, F), tile_group, E, torch.float32, gated=False)
+    y = torch.empty((T, K), dtype=torch.float32, device=dev)
+    ops._check(lib.tb_moe_combine(ops._stream(), ops._ptr(part), ops._ptr(weights), ops._ptr(position), ops._ptr(y), T, top, K),
+               "moe_combine")
+    return y
 
 
 def experts(x: torch.Tensor, gate_up: torch.Tensor, down: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor) -> torch.Tensor:
@@ -56,6 +91,8 @@ def experts(x: torch.Tensor, gate_up: torch.Tensor, down: torch.Tensor, ids: tor
     if K2 != K or tuple(down.shape) != (E, K, F) or tuple(ids.shape) != (T, top) or tuple(weights.shape) != (T, top):
         raise ops.KernelError(f"x {tuple(x.shape)}, gate_up {tuple(gate_up.shape)}, down {tuple(down.shape)}, ids "
                               f"{tuple(ids.shape)} do not fit together")
+    if wide_applies(x, K, F, top, E):
+        return _experts_wide(x, gate_up, down, ids, weights)
     y = torch.empty((T, K), dtype=torch.float32, device=x.device)
     lib = load_library("moe")
     if tiles_apply(x, K, F):
@@ -71,11 +108,17 @@ def experts(x: torch.Tensor, gate_up: torch.Tensor, down: torch.Tensor, ids: tor
         ops.launches += 3  # four kernels
         return y
     step = max(1, _MAX_SLOTS // top)
+    offsets = torch.empty(E + 1, dtype=torch.int32, device=x.device)
     for t0 in range(0, T, step):
         n = min(step, T - t0)
+        order = torch.empty(n * top, dtype=torch.int32, device=x.device)
         act = torch.empty((n * top, F), dtype=x.dtype, device=x.device)
-        ops._check(lib.tb_moe_gate_up(ops._stream(), ops._ptr(x[t0:]), ops._ptr(gate_up), ops._ptr(ids[t0:]), ops._ptr(act), n, top, F,
-                                      K, ops._code(x.dtype)), "moe_gate_up")
-        ops._check(lib.tb_moe_down(ops._stream(), ops._ptr(act), ops._ptr(down), ops._ptr(ids[t0:]), ops._ptr(weights[t0:]),
-                                   ops._ptr(y[t0:]), n, top, K, F, ops._code(x.dtype)), "moe_down")
+        part = torch.empty((n * top, K), dtype=torch.float32, device=x.device)
+        ops._check(lib.tb_moe_order(ops._stream(), ops._ptr(ids[t0:]), ops._ptr(offsets), ops._ptr(order), n, top, E), "moe_order")
+        ops._check(lib.tb_moe_gate_up(ops._stream(), ops._ptr(x[t0:]), ops._ptr(gate_up), ops._ptr(ids[t0:]), ops._ptr(order),
+                                      ops._ptr(act), n, top, F, K, ops._code(x.dtype)), "moe_gate_up")
+        ops._check(lib.tb_moe_down(ops._stream(), ops._ptr(act), ops._ptr(down), ops._ptr(ids[t0:]), ops._ptr(order), ops._ptr(part),
+                                   n, top, K, F, ops._code(x.dtype)), "moe_down")
+        ops._check(lib.tb_moe_combine(ops._stream(), ops._ptr(part), ops._ptr(weights[t0:]), ops._ptr(None), ops._ptr(y[t0:]), n, top, K),
+                   "moe_combine")
     return y

@@ -238,12 +238,12 @@ def test_the_scan_with_a_decay_per_token_and_shared_keys():
 
 @pytest.mark.parametrize("top,experts,ff,width", [(2, 6, 24, 64), (1, 3, 40, 48), (4, 9, 16, 96)])
 def test_the_expert_kernels_agree(top, experts, ff, width):
-    """Routing against the plain choice; the kernel of one warp per output and the sorted tiles on the tensor cores
-    against float64, for token counts around a tile's edge."""
+    """Routing against the plain choice; the kernel of one warp per output, the sorted tiles on mma.sync and the grouped
+    tcgen05 product (from 256 tokens on) against float64, for token counts around a tile's edge."""
     from tandem_b200.kernels import moe
 
     g = torch.Generator().manual_seed(top)
-    for T in (1, 5, 63, 64, 65, 200):
+    for T in (1, 5, 63, 64, 65, 200, 300, 700):
         x = (torch.randn(T, width, generator=g)).to(torch.bfloat16)
         gate_up = (torch.randn(experts, 2 * ff, width, generator=g) * 0.2).to(torch.bfloat16)
         down = (torch.randn(experts, width, ff, generator=g) * 0.2).to(torch.bfloat16)
@@ -254,12 +254,14 @@ def test_the_expert_kernels_agree(top, experts, ff, width):
         want = val / (val.sum(-1, keepdim=True) + 1e-20) * 1.5
         assert (weights.cpu().double().sort(-1).values - want.sort(-1).values).abs().max() < 1e-6
         ref = torch.zeros(T, width, dtype=torch.float64)
-        for t in range(T):
-            for k in range(top):
-                e = int(ids[t, k])
-                ref[t] += float(weights[t, k]) * plain.gated_ff(x[t: t + 1].double(), gate_up[e, :ff].double(), gate_up[e, ff:].double(), down[e].double())[0]
+        ids_host, weights_host = ids.cpu(), weights.cpu().double()
+        for e in range(experts):  # expert by expert, all its tokens at once
+            rows, ks = (ids_host == e).nonzero(as_tuple=True)
+            if len(rows):
+                out = plain.gated_ff(x[rows].double(), gate_up[e, :ff].double(), gate_up[e, ff:].double(), down[e].double())
+                ref.index_add_(0, rows, weights_host[rows, ks][:, None] * out)
         scale = float(ref.abs().max())
-        for mode in ("simt", "tiles"):
+        for mode in ("simt", "tiles", "wide"):
             os.environ["TANDEM_MOE"] = mode
             try:
                 got = moe.experts(x.cuda(), gate_up.cuda(), down.cuda(), ids, weights).cpu().double()
