@@ -255,17 +255,30 @@ __global__ void decay_recurrence_post_kernel(const float* __restrict__ o, const 
 // channels u = [x: inner | B: G N | C: G N] and inner = H P.  One thread per (token, channel):
 //   c_t = SiLU(bias + sum_j taps[K-1-j] u_(t-j)),  u before this step's first token from the request's state
 //   (the inputs at positions start-(K-1) .. start-1, zeros in front of the sequence), float32 [slots][K-1][C].
-// Written to rows [x | B | C | dt x] (stride 2 inner + 2 G N) for the scan and the epilogue; the first thread
-// of a head also writes the head's decay exp(-exp(A_log) dt) with dt = softplus(dt + dt_bias).
+// Written to rows [x | B | C | dt x] (stride 2 inner + 2 G N) for the scan and the epilogue.  dt = softplus(dt + dt_bias)
+// and the heads' decays exp(-exp(A_log) dt) are made once per (token, head) by a small kernel in front.
 __device__ __forceinline__ float softplus_f(float x) { return fmaxf(x, 0.f) + log1pf(expf(-fabsf(x))); }
 
+// One thread per (token, head): dt = softplus(dt + dt_bias) and the head's decay exp(-exp(A_log) dt).
+__global__ void selective_step_kernel(const float* __restrict__ proj, int stride, int dt_col, const float* __restrict__ dt_bias,
+                                      const float* __restrict__ a_log, float* __restrict__ dt_out, float* __restrict__ decay, int total,
+                                      int H) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= total) return;
+  const int t = idx / H, h = idx % H;
+  const float dt = softplus_f(proj[(size_t)t * stride + dt_col + h] + dt_bias[h]);
+  dt_out[idx] = dt;
+  decay[idx] = expf(-expf(a_log[h]) * dt);
+}
+
 __global__ void selective_prep_kernel(const float* __restrict__ proj, int stride, const float* __restrict__ taps,
-                                      const float* __restrict__ conv_bias, const float* __restrict__ dt_bias,
-                                      const float* __restrict__ a_log, const float* __restrict__ conv_state, long long state_stride,
+                                      const float* __restrict__ conv_bias, const float* __restrict__ dt,
+                                      const float* __restrict__ conv_state, long long state_stride,
                                       const int* __restrict__ seq_of_token, const int* __restrict__ positions,
                                       const int* __restrict__ seq_starts, const int* __restrict__ state_slots,
-                                      float* __restrict__ rows, float* __restrict__ decay, long long total, int H, int P, int GN2,
-                                      int K) {
+                                      float* __restrict__ rows, long long total, int H, int P, int GN2, int K) {
   pdl_launch_dependents();
   pdl_wait();
   const int inner = H * P, C = inner + GN2, out_stride = 2 * inner + GN2;
@@ -282,12 +295,7 @@ __global__ void selective_prep_kernel(const float* __restrict__ proj, int stride
     const float v = acc / (1.f + expf(-acc));
     float* row = rows + (size_t)t * out_stride;
     row[c] = v;
-    if (c < inner) {
-      const int h = c / P;
-      const float dt = softplus_f(proj[(size_t)t * stride + inner + C + h] + dt_bias[h]);
-      row[inner + GN2 + c] = dt * v;
-      if (c == h * P) decay[(size_t)t * H + h] = expf(-expf(a_log[h]) * dt);
-    }
+    if (c < inner) row[inner + GN2 + c] = dt[(size_t)t * H + c / P] * v;
   }
 }
 
@@ -311,6 +319,8 @@ __global__ void conv_state_update_kernel(const float* __restrict__ proj, int str
 
 // y = (o + D_h x) * SiLU(z), divided by its root mean square in `parts` equal parts of the row, times weight.
 // grid (tokens, parts).  o float32 [T, H P]; x at rows[t][0 .. H P); z at proj[t][0 .. H P).
+constexpr int SP_KEEP = 8;  // values a thread keeps between the two passes
+
 template <typename T>
 __global__ void selective_post_kernel(const float* __restrict__ o, const float* __restrict__ rows, int rows_stride,
                                       const float* __restrict__ z, int z_stride, const float* __restrict__ D,
@@ -322,14 +332,35 @@ __global__ void selective_post_kernel(const float* __restrict__ o, const float* 
   const float* orow = o + (size_t)t * H * P;
   const float* xrow = rows + (size_t)t * rows_stride;
   const float* zrow = z + (size_t)t * z_stride;
+  const bool keep = n <= SP_KEEP * (int)blockDim.x;  // else the second pass computes the values again
+  float held[SP_KEEP];
   float ss = 0.f;
-  for (int c = c0 + threadIdx.x; c < c0 + n; c += blockDim.x) {
-    const float zz = zrow[c];
-    const float v = fmaf(D[c / P], xrow[c], orow[c]) * (zz / (1.f + expf(-zz)));
-    ss = fmaf(v, v, ss);
+#pragma unroll
+  for (int i = 0; i < SP_KEEP; ++i) {
+    const int c = c0 + threadIdx.x + i * blockDim.x;
+    held[i] = 0.f;
+    if (keep && c < c0 + n) {
+      const float zz = zrow[c];
+      held[i] = fmaf(D[c / P], xrow[c], orow[c]) * (zz / (1.f + expf(-zz)));
+      ss = fmaf(held[i], held[i], ss);
+    }
   }
+  if (!keep)
+    for (int c = c0 + threadIdx.x; c < c0 + n; c += blockDim.x) {
+      const float zz = zrow[c];
+      const float v = fmaf(D[c / P], xrow[c], orow[c]) * (zz / (1.f + expf(-zz)));
+      ss = fmaf(v, v, ss);
+    }
   ss = block_sum(ss, scratch);
   const float inv = rsqrtf(ss / (float)n + eps);
+  if (keep) {
+#pragma unroll
+    for (int i = 0; i < SP_KEEP; ++i) {
+      const int c = c0 + threadIdx.x + i * blockDim.x;
+      if (c < c0 + n) y[(size_t)t * H * P + c] = from_float<T>(held[i] * inv * weight[c]);
+    }
+    return;
+  }
   for (int c = c0 + threadIdx.x; c < c0 + n; c += blockDim.x) {
     const float zz = zrow[c];
     const float v = fmaf(D[c / P], xrow[c], orow[c]) * (zz / (1.f + expf(-zz)));
@@ -385,18 +416,23 @@ int tb_decay_recurrence_scan(void* stream, const float* proj, int stride, const 
 }
 
 // proj float32 [T, stride >= 2 H P + GN2 + H]; taps [H P + GN2, K]; conv_state: slot s at conv_state + s * state_stride,
-// [K - 1][H P + GN2]; rows float32 [T, 2 H P + GN2] = [x | B | C | dt x]; decay float32 [T, H].
+// [K - 1][H P + GN2]; rows float32 [T, 2 H P + GN2] = [x | B | C | dt x]; decay and dt float32 [T, H].
 int tb_selective_prep(void* stream, const float* proj, int stride, const float* taps, const float* conv_bias, const float* dt_bias,
                       const float* a_log, const float* conv_state, long long state_stride, const int* seq_of_token,
-                      const int* positions, const int* seq_starts, const int* state_slots, float* rows, float* decay, int T_tokens,
-                      int H, int P, int GN2, int K) {
+                      const int* positions, const int* seq_starts, const int* state_slots, float* rows, float* decay, float* dt,
+                      int T_tokens, int H, int P, int GN2, int K) {
   if (T_tokens <= 0) return 0;
   if (H <= 0 || P <= 0 || GN2 < 0 || K <= 0 || stride < 2 * H * P + GN2 + H) return TB_ERR_BAD_SIZE;
+  if ((long long)T_tokens * H > 0x7fffffffLL) return TB_ERR_BAD_SIZE;
+  const int steps = T_tokens * H;
+  int rc = tb::launch(tb::selective_step_kernel, dim3((steps + 255) / 256), dim3(256), 0, stream, proj, stride, 2 * H * P + GN2, dt_bias,
+                      a_log, dt, decay, steps, H);
+  if (rc != 0) return rc;
   const long long total = (long long)T_tokens * (H * P + GN2);
   long long blocks = (total + 255) / 256;
-  if (blocks > 148 * 16) blocks = 148 * 16;
-  return tb::launch(tb::selective_prep_kernel, dim3((int)blocks), dim3(256), 0, stream, proj, stride, taps, conv_bias, dt_bias, a_log,
-                    conv_state, state_stride, seq_of_token, positions, seq_starts, state_slots, rows, decay, total, H, P, GN2, K);
+  if (blocks > 148 * 64) blocks = 148 * 64;
+  return tb::launch(tb::selective_prep_kernel, dim3((int)blocks), dim3(256), 0, stream, proj, stride, taps, conv_bias, (const float*)dt,
+                    conv_state, state_stride, seq_of_token, positions, seq_starts, state_slots, rows, total, H, P, GN2, K);
 }
 
 int tb_conv_state_update(void* stream, const float* proj, int stride, int col0, float* conv_state, long long state_stride,
@@ -412,7 +448,9 @@ int tb_selective_post(void* stream, const float* o, const float* rows, int rows_
                       const float* weight, void* y, int T_tokens, int H, int P, int parts, float eps, int dtype) {
   if (T_tokens <= 0) return 0;
   if (H <= 0 || P <= 0 || parts <= 0 || (H * P) % parts || parts > 65535) return TB_ERR_BAD_SIZE;
-  TB_DISPATCH_DTYPE(dtype, tb::launch(tb::selective_post_kernel<T>, dim3(T_tokens, parts), dim3(256), 0, stream, o, rows, rows_stride,
+  const int n = H * P / parts;
+  const int threads = n >= 8192 ? 1024 : n >= 2048 ? 512 : 256;
+  TB_DISPATCH_DTYPE(dtype, tb::launch(tb::selective_post_kernel<T>, dim3(T_tokens, parts), dim3(threads), 0, stream, o, rows, rows_stride,
                                       z, z_stride, D, weight, (T*)y, H, P, parts, eps));
 }
 

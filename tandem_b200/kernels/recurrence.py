@@ -143,13 +143,15 @@ def selective_prepare(proj: torch.Tensor, taps: torch.Tensor, conv_bias: torch.T
         raise ops.KernelError("the convolution's inputs do not fit into the state row")
     rows = torch.empty((T, 2 * inner + group_cols), dtype=torch.float32, device=proj.device)
     decay = torch.empty((T, num_heads), dtype=torch.float32, device=proj.device)
+    steps = torch.empty((T, num_heads), dtype=torch.float32, device=proj.device)
     lib = load_library("decay_recurrence")
     conv_state = ctypes.c_void_p(state.data_ptr() + 4 * conv_offset)
     ops._check(lib.tb_selective_prep(ops._stream(), ops._ptr(proj), proj.stride(0), ops._ptr(taps), ops._ptr(conv_bias),
                                      ops._ptr(dt_bias), ops._ptr(a_log), conv_state, ctypes.c_longlong(per_slot),
                                      ops._ptr(ctx.seq_of_token), ops._ptr(ctx.positions), ops._ptr(ctx.seq_starts),
-                                     ops._ptr(ctx.state_slots), ops._ptr(rows), ops._ptr(decay), T, num_heads, value_dim,
-                                     group_cols, num_taps), "selective_prep")
+                                     ops._ptr(ctx.state_slots), ops._ptr(rows), ops._ptr(decay), ops._ptr(steps), T, num_heads,
+                                     value_dim, group_cols, num_taps), "selective_prep")
+    ops.launches += 1  # two kernels
     return rows, decay
 
 
