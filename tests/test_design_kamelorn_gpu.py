@@ -484,6 +484,27 @@ def test_random_models_and_schedules(tmp_path, seed):
                 assert distance(got[rid], ref[rid]) < LIMIT[dtype], (cfg, page_size, regime, dtype, rid)
 
 
+def test_a_model_of_middling_sizes(tmp_path):
+    """Sizes beyond the tiny ones: a latent wider than the tensor-core tile kernel takes (keys of 160 + 32, values of 160), sixteen
+    heads over the one key head, sixteen state-space heads, nine experts of which three are chosen, a prompt long enough for the
+    grouped product, and portions beside decoded tokens of other requests."""
+    cfg = model_config([mamba_layer(heads=16, vdim=32, state=64, groups=4, conv=4, norm_groups=2, mlp=routed(ff=96, experts=9, top=3, scale=1.0)),
+                        latent_layer(heads=16, dim=32, rot_dim=32, vdim=24, kv_rank=160, scale=0.07, base=1e5, mlp=dense(640)),
+                        latent_layer(heads=8, dim=48, rot_dim=16, vdim=32, kv_rank=112, scale=0.09, base=1e4, mlp=routed(ff=64, experts=4, top=2))],
+                       width=384, vocab=700, streams=3, loop=(0, 2, 2), mult=0.6)
+    folder = make_folder(tmp_path, cfg, std=0.04)
+    requests = {"a": tokens(71, 420, 700), "b": tokens(72, 130, 700), "c": tokens(73, 67, 700)}
+    ref = reference(folder, requests)
+    for dtype in ("float32", "bfloat16"):
+        for steps in (rc.whole(requests), rc.mixed(requests, live=3, portion=40, decode_after=0.8)):
+            got = run_steps(folder, dtype, steps, page_size=16)
+            for rid in requests:
+                if dtype == "bfloat16":
+                    assert close_but_for_router_flips(got[rid], ref[rid]), (dtype, rid)
+                else:
+                    assert distance(got[rid], ref[rid]) < LIMIT[dtype], (dtype, rid)
+
+
 # ----------------------------------------------------------------------------- through the engine's entry point
 @pytest.mark.parametrize("options", [dict(), dict(cuda_graph=False, overlap_schedule=False), dict(max_num_batched_tokens=16, max_num_seqs=2)])
 def test_greedy_generation_through_the_engine(tmp_path, options):
