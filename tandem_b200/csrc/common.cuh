@@ -101,7 +101,7 @@ inline bool pdl_enabled() {
 }
 
 template <typename... KArgs, typename... Args>
-inline int launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, void* stream, Args&&... args) {
+inline int launch_with(bool early, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, void* stream, Args&&... args) {
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = grid;
   cfg.blockDim = block;
@@ -109,10 +109,23 @@ inline int launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, 
   cfg.stream = (cudaStream_t)stream;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[0].val.programmaticStreamSerializationAllowed = pdl_enabled() ? 1 : 0;
+  attr[0].val.programmaticStreamSerializationAllowed = (early && pdl_enabled()) ? 1 : 0;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
   return (int)cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
+template <typename... KArgs, typename... Args>
+inline int launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, void* stream, Args&&... args) {
+  return launch_with(true, kernel, grid, block, smem, stream, static_cast<Args&&>(args)...);
+}
+
+// For the kernels that stand directly behind a copy from the host in the stream (a step's batch description): they are
+// launched in plain stream order, behind everything in front of them, the copy included.  Letting them become resident
+// early buys nothing there, and their inputs are what that copy brings.
+template <typename... KArgs, typename... Args>
+inline int launch_in_order(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, void* stream, Args&&... args) {
+  return launch_with(false, kernel, grid, block, smem, stream, static_cast<Args&&>(args)...);
 }
 
 }  // namespace tb

@@ -515,7 +515,7 @@ int tb_embedding(void* stream, const int* ids, const void* table, float* out, in
                  int dtype, float scale, const int* positions, const void* pos_table, int max_pos, int copies) {
   if (T_tokens <= 0) return 0;
   if ((pos_table && (!positions || max_pos <= 0)) || copies <= 0 || copies > 65535) return TB_ERR_BAD_SIZE;
-  TB_DISPATCH_DTYPE(dtype, tb::launch(tb::embedding_kernel<T>, dim3(T_tokens, copies), dim3(256), 0, stream, ids, (const T*)table, out, H, V,
+  TB_DISPATCH_DTYPE(dtype, tb::launch_in_order(tb::embedding_kernel<T>, dim3(T_tokens, copies), dim3(256), 0, stream, ids, (const T*)table, out, H, V,
                                       scale, positions, (const T*)pos_table, max_pos));
 }
 
@@ -529,7 +529,7 @@ int tb_scale_softcap(void* stream, float* logits, long long n, float scale, floa
 
 int tb_take_tokens(void* stream, int* ids, const int* source, const int* tokens, int n, int num_tokens) {
   if (n <= 0) return 0;
-  return tb::launch(tb::take_tokens_kernel, dim3((n + 127) / 128), dim3(128), 0, stream, ids, source, tokens, n, num_tokens);
+  return tb::launch_in_order(tb::take_tokens_kernel, dim3((n + 127) / 128), dim3(128), 0, stream, ids, source, tokens, n, num_tokens);
 }
 
 int tb_add_rmsnorm(void* stream, const void* x, float* residual, const float* weight, void* y, const int* rows,
